@@ -1,0 +1,28 @@
+// Error text, environment switches and version of libhfrk_b200.so.
+#include "host_common.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+namespace hfrk {
+
+namespace {
+thread_local std::string g_last_error;
+}
+
+void set_last_error(const char* text) { g_last_error = text ? text : ""; }
+
+int default_use_pdl() {
+    static const int value = [] {
+        const char* env = std::getenv("HFRK_PDL");
+        return (env != nullptr && std::strcmp(env, "1") == 0) ? 1 : 0;
+    }();
+    return value;
+}
+
+}  // namespace hfrk
+
+extern "C" const char* hfrk_last_error(void) { return hfrk::g_last_error.c_str(); }
+
+extern "C" int hfrk_version(void) { return 100; }

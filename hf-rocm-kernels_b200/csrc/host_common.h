@@ -1,0 +1,29 @@
+// Host-side helpers shared by the translation units of libhfrk_b200.so: the per-thread error
+// text behind hfrk_last_error() and the CUDA-call check that turns a failure into a status code
+// (the library reports by return value, like the reference's launcher:
+// csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:9-17).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/hfrk_b200.h"
+
+namespace hfrk {
+
+void set_last_error(const char* text);
+
+// 1 when the environment asks for programmatic dependent launch on the plain entry point
+// (HFRK_PDL=1). Off by default: it is only safe when nothing earlier on the stream writes W.
+int default_use_pdl();
+
+}  // namespace hfrk
+
+#define HFRK_CUDA_TRY(expr)                                      \
+    do {                                                         \
+        cudaError_t hfrk_err_ = (expr);                          \
+        if (hfrk_err_ != cudaSuccess) {                          \
+            ::hfrk::set_last_error(cudaGetErrorString(hfrk_err_)); \
+            (void)cudaGetLastError();                            \
+            return HFRK_CUDA_ERROR;                              \
+        }                                                        \
+    } while (0)

@@ -1,0 +1,633 @@
+// FP8 skinny GEMM for B200 (sm_100a):  D[m,n] <- D_in[m,n] + scale * sum_k A[m,k] * W[n,k].
+//
+// The operation is bound by the one pass over the weight matrix W (N*K bytes from HBM); the token
+// count M is tiny. The kernel is therefore a weight streamer with a tensor-core sink:
+//
+//   * swap-AB: a CTA owns 128 consecutive rows of W. Those rows are the M=128 side of a
+//     tcgen05.mma (kind::f8f6f4, e4m3 x e4m3 -> f32); the padded token count (16..64) is the MMA
+//     N side. The accumulator D^T[128 x m_pad] lives in TMEM, one W row per TMEM lane.
+//   * one elected thread streams 128x128-byte W boxes (and the matching m_pad x 128-byte A boxes)
+//     with TMA, 128-byte swizzled, into a ring of shared-memory stages guarded by full/empty
+//     mbarriers; one elected thread issues four K=32 MMAs per stage and commits the stage back to
+//     the producer; four warps drain TMEM and write D.
+//   * split-K across a thread-block cluster when N/128 tiles cannot fill the SMs: each CTA of the
+//     cluster reduces a slice of the 128 x M partial tile out of its peers' shared memory (DSMEM)
+//     in a fixed rank order, so the result is deterministic (the reference uses fp16 atomics:
+//     csrc/op_src/skinny_gemm/consumers/mfma_16x16x32_consumer.cu:113-168).
+//   * every wait on an mbarrier is bounded; a wait that runs out records a status word, lets the
+//     other roles give up too, and the CTA still frees its TMEM and leaves normally.
+//   * programmatic dependent launch: the weight stream of a call may start before the previous
+//     kernel on the stream has finished, because W is static; A and D are only touched after
+//     griddepcontrol.wait.
+//
+// Role of this file in the reference's terms: it replaces skinny_gemm_kernel.cu:6-79 (kernel),
+// producers/*.cu (global->LDS streaming), consumers/*.cu (MFMA + atomic epilogue) and
+// skinny_gemm_caller.cu:21-71 (validation, launch shape) of csrc/op_src/skinny_gemm/.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "../../include/hfrk_b200.h"
+#include "host_common.h"
+#include "ptx_sm100.cuh"
+
+namespace hfrk {
+
+constexpr int kTileN = 128;                        // W rows per CTA  (tcgen05.mma M)
+constexpr int kBlockK = 128;                       // fp8 elements per stage row = one swizzle atom
+constexpr int kUmmaK = 32;                         // K of one tcgen05.mma for 8-bit operands
+constexpr int kWStageBytes = kTileN * kBlockK;     // 16 KiB of W per stage
+constexpr int kMaxStages = 12;
+constexpr int kThreads = 192;                      // 4 epilogue warps + producer warp + MMA warp
+constexpr int kEpilogueThreads = 128;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kMaxMPad = 64;                       // tokens per launch (larger M loops on the host)
+constexpr int kMaxSplit = 16;
+constexpr int kSmemLimit = 227 * 1024;
+constexpr int kNumSms = 148;
+constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds of SM clock
+
+enum Role : int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3 };
+
+struct Ctrl {
+    uint64_t full[kMaxStages];    // TMA -> MMA : stage holds data
+    uint64_t empty[kMaxStages];   // MMA -> TMA : stage may be overwritten
+    uint64_t accum;               // MMA -> epilogue : accumulator complete
+    uint32_t tmem_base;
+    volatile uint32_t abort;      // set by the first role whose wait ran out
+};
+constexpr int kCtrlBytes = 256;
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
+
+struct GemmParams {
+    void* d;
+    const float* scale;
+    float kind_factor;   // 0.5 per e4m3fnuz operand
+    int m, n, k;
+    int m_pad;           // MMA N: m rounded up to 16
+    int num_kblocks;     // ceil(k / 128)
+    int split;           // CTAs per cluster along K
+    int stages;
+    int d_dtype;
+    int accumulate;
+};
+
+// Device-side status of this library on the current device. Written only when a bounded wait
+// runs out; read and cleared by hfrk_device_status().
+__device__ unsigned int g_device_status = 0;
+
+__device__ __forceinline__ void record_timeout(int role) {
+    const unsigned int word = (static_cast<unsigned int>(HFRK_DEVICE_TIMEOUT) << 24) |
+                              (static_cast<unsigned int>(role) << 16) | (blockIdx.x & 0xffffu);
+    atomicCAS(&g_device_status, 0u, word);
+}
+
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                            int role) {
+    const long long start = clock64();
+    for (;;) {
+        for (int i = 0; i < 32; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (*abort_flag) return false;
+        if (clock64() - start > kWaitLimitCycles) {
+            *abort_flag = 1u;
+            record_timeout(role);
+            return false;
+        }
+    }
+}
+
+// Waits for the phase with the given parity to complete; false if the wait ran out or another
+// role of this CTA already gave up.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  int role) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, role);
+}
+
+__device__ __forceinline__ float load_out(const void* d, size_t idx, int dtype) {
+    return dtype == HFRK_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(d)[idx])
+                              : __half2float(static_cast<const __half*>(d)[idx]);
+}
+
+__device__ __forceinline__ void store_out(void* d, size_t idx, int dtype, float v) {
+    if (dtype == HFRK_BF16) {
+        static_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
+    } else {
+        static_cast<__half*>(d)[idx] = __float2half_rn(v);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                             const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // The swizzled operand tiles need 1024-byte alignment; dynamic shared memory only promises 16.
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t ring_addr = (raw_addr + 1023u) & ~1023u;
+    uint8_t* const ring_ptr = smem_raw + (ring_addr - raw_addr);
+    const uint32_t a_bytes = static_cast<uint32_t>(p.m_pad) * kBlockK;
+    const uint32_t stage_bytes = kWStageBytes + a_bytes;
+    Ctrl* const ctrl = reinterpret_cast<Ctrl*>(ring_ptr + static_cast<size_t>(p.stages) * stage_bytes);
+    const uint32_t full_bar = smem_u32(&ctrl->full[0]);
+    const uint32_t empty_bar = smem_u32(&ctrl->empty[0]);
+    const uint32_t accum_bar = smem_u32(&ctrl->accum);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kTileN;
+
+    // K blocks of this CTA: a contiguous range, the remainder spread over the first ranks.
+    const int rank = p.split > 1 ? static_cast<int>(cluster_cta_rank()) : 0;
+    const int kb_base = p.num_kblocks / p.split;
+    const int kb_rem = p.num_kblocks % p.split;
+    const int kb_count = kb_base + (rank < kb_rem ? 1 : 0);
+    const int kb_start = rank * kb_base + (rank < kb_rem ? rank : kb_rem);
+    const int prologue = kb_count < p.stages ? kb_count : p.stages;
+
+    const uint32_t tmem_cols = p.m_pad <= 32 ? 32u : 64u;
+    uint64_t pol_w = 0, pol_a = 0;
+
+    if (warp == kProducerWarp) {
+        if (lane == 0) {
+            prefetch_tensormap(&tmap_w);
+            prefetch_tensormap(&tmap_a);
+            ctrl->abort = 0u;
+            for (int s = 0; s < p.stages; ++s) {
+                mbar_init(full_bar + 8u * s, 1);
+                mbar_init(empty_bar + 8u * s, 1);
+            }
+            mbar_init(accum_bar, 1);
+            mbar_init_fence();
+            pol_w = l2_policy_evict_first();
+            pol_a = l2_policy_evict_last();
+            // Start the weight stream before anything else in the CTA is ready: W does not depend
+            // on the previous kernel, A does.
+            for (int i = 0; i < prologue; ++i) {
+                mbar_arrive_expect_tx(full_bar + 8u * i, stage_bytes);
+                tma_load_2d(ring_addr + i * stage_bytes, &tmap_w, full_bar + 8u * i, (kb_start + i) * kBlockK, n0,
+                            pol_w);
+            }
+            pdl_wait_prior_grids();
+            for (int i = 0; i < prologue; ++i) {
+                tma_load_2d(ring_addr + i * stage_bytes + kWStageBytes, &tmap_a, full_bar + 8u * i,
+                            (kb_start + i) * kBlockK, 0, pol_a);
+            }
+        }
+        __syncwarp();
+    } else if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), tmem_cols);
+        tmem_relinquish_alloc_permit();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    pdl_launch_dependents();
+    const uint32_t tmem_acc = ctrl->tmem_base;
+
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int issued = prologue;
+            for (int i = prologue; i < kb_count; ++i) {
+                const int s = i % p.stages;
+                const uint32_t round = static_cast<uint32_t>(i / p.stages);
+                if (!mbar_wait_bounded(empty_bar + 8u * s, (round - 1u) & 1u, &ctrl->abort, kRoleProducer)) break;
+                mbar_arrive_expect_tx(full_bar + 8u * s, stage_bytes);
+                tma_load_2d(ring_addr + s * stage_bytes, &tmap_w, full_bar + 8u * s, (kb_start + i) * kBlockK, n0,
+                            pol_w);
+                tma_load_2d(ring_addr + s * stage_bytes + kWStageBytes, &tmap_a, full_bar + 8u * s,
+                            (kb_start + i) * kBlockK, 0, pol_a);
+                issued = i + 1;
+            }
+            if (ctrl->abort) {
+                // Give the copies already in flight a bounded chance to land before the CTA exits.
+                for (int s = 0; s < p.stages && s < issued; ++s) {
+                    const int last = ((issued - 1 - s) / p.stages) * p.stages + s;
+                    const uint32_t parity = static_cast<uint32_t>(last / p.stages) & 1u;
+                    const long long start = clock64();
+                    while (!mbar_try_wait(full_bar + 8u * s, parity)) {
+                        if (clock64() - start > kWaitLimitCycles / 8) break;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_e4m3_f32(kTileN, p.m_pad);
+            for (int i = 0; i < kb_count; ++i) {
+                const int s = i % p.stages;
+                const uint32_t round = static_cast<uint32_t>(i / p.stages);
+                if (!mbar_wait_bounded(full_bar + 8u * s, round & 1u, &ctrl->abort, kRoleMma)) break;
+                tcgen05_fence_after_sync();
+                const uint64_t w_desc = umma_desc_kmajor_sw128(ring_addr + s * stage_bytes);
+                const uint64_t a_desc = umma_desc_kmajor_sw128(ring_addr + s * stage_bytes + kWStageBytes);
+#pragma unroll
+                for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                    // +32 bytes along K inside the swizzle atom = +2 in the (address >> 4) field.
+                    umma_f8f6f4(tmem_acc, w_desc + 2u * kk, a_desc + 2u * kk, idesc, (i | kk) != 0 ? 1u : 0u);
+                }
+                umma_commit(empty_bar + 8u * s);
+            }
+            umma_commit(accum_bar);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 0..3)
+        pdl_wait_prior_grids();
+        const int nl = threadIdx.x;  // TMEM lane = W row inside the tile
+        const int n = n0 + nl;
+        const bool direct = p.split == 1;
+        const float scale = __ldg(p.scale) * p.kind_factor;
+        const uint32_t lane_taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
+
+        float din[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            din[j] = (direct && p.accumulate && j < p.m && n < p.n)
+                         ? load_out(p.d, static_cast<size_t>(j) * p.n + n, p.d_dtype)
+                         : 0.0f;
+        }
+
+        bool ok = mbar_wait_bounded(accum_bar, 0u, &ctrl->abort, kRoleEpilogue);
+        ok = __all_sync(0xffffffffu, ok) && ctrl->abort == 0u;
+        ok = __all_sync(0xffffffffu, ok);
+        tcgen05_fence_after_sync();
+        if (ok) {
+            float* const partial = reinterpret_cast<float*>(ring_ptr);
+            for (int c = 0; c < p.m_pad / 16; ++c) {
+                uint32_t v[16];
+                tmem_ld_32x32b_x16(lane_taddr + static_cast<uint32_t>(c * 16), v);
+                tmem_ld_wait();
+                if (direct) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = c * 16 + j;
+                        if (m < p.m && n < p.n) {
+                            const size_t idx = static_cast<size_t>(m) * p.n + n;
+                            const float d_in = c == 0 ? din[j] : (p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f);
+                            store_out(p.d, idx, p.d_dtype, fmaf(__uint_as_float(v[j]), scale, d_in));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        partial[(c * 16 + j) * kTileN + nl] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    if (p.split > 1) {
+        // Reduce-scatter of the split-K partial tiles through distributed shared memory: CTA `rank`
+        // finalises elements [rank*chunk, (rank+1)*chunk) of the m x 128 tile, reading every peer's
+        // copy (its own included) in rank order.
+        cluster_sync_all();
+        if (warp < kEpilogueThreads / 32 && ctrl->abort == 0u) {
+            const float scale = __ldg(p.scale) * p.kind_factor;
+            const int total = p.m * kTileN;
+            const int chunk = (total + p.split - 1) / p.split;
+            const int e_begin = rank * chunk;
+            const int e_end = e_begin + chunk < total ? e_begin + chunk : total;
+            for (int e = e_begin + static_cast<int>(threadIdx.x); e < e_end; e += kEpilogueThreads) {
+                float sum = 0.0f;
+                for (int q = 0; q < p.split; ++q) {
+                    sum += dsmem_ld_f32(dsmem_map(ring_addr + 4u * static_cast<uint32_t>(e), static_cast<uint32_t>(q)));
+                }
+                const int m = e / kTileN;
+                const int n = n0 + (e % kTileN);
+                if (n < p.n) {
+                    const size_t idx = static_cast<size_t>(m) * p.n + n;
+                    const float d_in = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
+                    store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d_in));
+                }
+            }
+        }
+        cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
+    }
+
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) tmem_dealloc(tmem_acc, tmem_cols);
+}
+
+// =============================================================================== host side
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres = cudaDriverEntryPointSymbolNotFound;
+        cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+        if (err != cudaSuccess || qres != cudaDriverEntryPointSuccess) ptr = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+struct MapKey {
+    const void* base;
+    uint64_t inner, outer, stride;
+    uint32_t box_outer;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box_outer == o.box_outer;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.inner + 0x632BE59BD9B4E019ull) + (h << 6) + (h >> 2);
+        h ^= (k.outer * 0xD6E8FEB86659FD93ull) + (h << 6) + (h >> 2);
+        h ^= (k.stride * 0xA24BAED4963EE407ull) + (h << 6) + (h >> 2);
+        h ^= k.box_outer;
+        return static_cast<size_t>(h);
+    }
+};
+
+// Encoding a tensor map costs a driver call; decode loops call the GEMM with the same weight
+// pointers every step, so descriptors are cached by (pointer, extents, pitch, box). The cache
+// holds no ownership: a stale entry for a freed-and-reused pointer is still a correct descriptor
+// for that address range.
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+// 2-D uint8 tensor [outer][inner] with a pitch of `stride` bytes, boxes of 128 x box_outer bytes,
+// 128-byte swizzle, zero fill outside the tensor.
+int get_tensor_map(const void* base, uint64_t inner, uint64_t outer, uint64_t stride, uint32_t box_outer,
+                   CUtensorMap* out) {
+    MapKey key{base, inner, outer, stride, box_outer};
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        auto it = g_map_cache.find(key);
+        if (it != g_map_cache.end()) {
+            *out = it->second;
+            return HFRK_SUCCESS;
+        }
+    }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+        return HFRK_CUDA_ERROR;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {stride};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_outer};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult res = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) {
+        char msg[256];
+        snprintf(msg, sizeof(msg),
+                 "cuTensorMapEncodeTiled failed (%d): base=%p inner=%llu outer=%llu pitch=%llu box=128x%u",
+                 static_cast<int>(res), base, static_cast<unsigned long long>(inner),
+                 static_cast<unsigned long long>(outer), static_cast<unsigned long long>(stride), box_outer);
+        set_last_error(msg);
+        return HFRK_CUDA_ERROR;
+    }
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (g_map_cache.size() > 8192) g_map_cache.clear();
+    g_map_cache.emplace(key, *out);
+    return HFRK_SUCCESS;
+}
+
+struct Plan {
+    int split, stages, ctas, smem_bytes, m_pad, num_kblocks;
+};
+
+int round_up(int v, int to) { return (v + to - 1) / to * to; }
+
+// Launch shape for one launch of m <= kMaxMPad tokens.
+//   split  : enough K splits that tiles * split covers the SMs, never leaving a split fewer than
+//            four K blocks (a split that short is all pipeline fill).
+//   stages : when the grid fits one CTA per SM the ring takes all of shared memory (12 stages at
+//            m_pad 16), which also keeps the CTAs of a cluster on different SMs; larger grids use
+//            half of it so two CTAs share an SM and one's epilogue overlaps the other's stream.
+int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
+    if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
+    if (split_req < 0 || split_req > kMaxSplit || stages_req < 0 || stages_req == 1 || stages_req > kMaxStages)
+        return HFRK_INVALID_CONFIG;
+    const int m_pad = round_up(m, 16);
+    const int tiles = (n + kTileN - 1) / kTileN;
+    const int nkb = (k + kBlockK - 1) / kBlockK;
+    const int stage_bytes = kWStageBytes + m_pad * kBlockK;
+    const int max_stages_fit = (kSmemLimit - 1024 - kCtrlBytes) / stage_bytes;
+
+    int split = split_req;
+    if (split == 0) {
+        split = 1;
+        const int by_depth = nkb / 4 > 1 ? nkb / 4 : 1;
+        while (split < 8 && split < by_depth && tiles * split < 128) ++split;
+    }
+    if (split > nkb) split = nkb;
+
+    const int ctas = tiles * split;
+    int stages = stages_req;
+    const bool one_per_sm = ctas <= kNumSms;
+    if (stages == 0) {
+        stages = one_per_sm ? max_stages_fit : (kSmemLimit / 2 - 1024 - 1024 - kCtrlBytes) / stage_bytes;
+    }
+    if (stages > max_stages_fit) stages = max_stages_fit;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return HFRK_INVALID_CONFIG;
+
+    int smem = 1024 + stages * stage_bytes + kCtrlBytes;
+    // Fewer stages than half of shared memory would let several CTAs of one cluster pile onto one
+    // SM while others idle; keep the footprint above half when the grid is at most one wave.
+    if (one_per_sm && smem <= kSmemLimit / 2) smem = kSmemLimit / 2 + 1024;
+    plan->split = split;
+    plan->stages = stages;
+    plan->ctas = ctas;
+    plan->smem_bytes = smem;
+    plan->m_pad = m_pad;
+    plan->num_kblocks = nkb;
+    return HFRK_SUCCESS;
+}
+
+int prepare_device_once() {
+    static std::mutex mu;
+    static bool done[64] = {};
+    int dev = 0;
+    HFRK_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && done[dev]) return HFRK_SUCCESS;
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemLimit));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    if (dev >= 0 && dev < 64) done[dev] = true;
+    return HFRK_SUCCESS;
+}
+
+int validate(const void* A, const void* W, void* D, const float* scale_dev, int m, int n, int k,
+             int64_t w_row_stride, int a_kind, int w_kind, int d_dtype) {
+    if (A == nullptr || W == nullptr || D == nullptr || scale_dev == nullptr) return HFRK_INVALID_CONFIG;
+    if (m <= 0 || n <= 0 || k <= 0) return HFRK_INVALID_CONFIG;
+    if ((a_kind != HFRK_E4M3FN && a_kind != HFRK_E4M3FNUZ) || (w_kind != HFRK_E4M3FN && w_kind != HFRK_E4M3FNUZ))
+        return HFRK_BAD_DTYPE;
+    if (d_dtype != HFRK_F16 && d_dtype != HFRK_BF16) return HFRK_BAD_DTYPE;
+    if (k % 16 != 0) return HFRK_K_NOT_DIVISIBLE;
+    if (w_row_stride < k || w_row_stride % 16 != 0) return HFRK_BAD_ALIGNMENT;
+    if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) ||
+        (reinterpret_cast<uintptr_t>(D) & 1u) || (reinterpret_cast<uintptr_t>(scale_dev) & 3u))
+        return HFRK_BAD_ALIGNMENT;
+    return HFRK_SUCCESS;
+}
+
+int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, int m, int n, int k,
+                int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int split_req,
+                int stages_req, int use_pdl, cudaStream_t stream) {
+    int rc = validate(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype);
+    if (rc != HFRK_SUCCESS) return rc;
+    rc = prepare_device_once();
+    if (rc != HFRK_SUCCESS) return rc;
+
+    CUtensorMap tmap_w;
+    rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(w_row_stride),
+                        kTileN, &tmap_w);
+    if (rc != HFRK_SUCCESS) return rc;
+
+    const size_t out_elem = 2;
+    for (int m0 = 0; m0 < m; m0 += kMaxMPad) {
+        const int mc = m - m0 < kMaxMPad ? m - m0 : kMaxMPad;
+        Plan plan;
+        rc = make_plan(mc, n, k, split_req, stages_req, &plan);
+        if (rc != HFRK_SUCCESS) return rc;
+        const uint8_t* a_chunk = static_cast<const uint8_t*>(A) + static_cast<size_t>(m0) * k;
+        CUtensorMap tmap_a;
+        rc = get_tensor_map(a_chunk, static_cast<uint64_t>(k), static_cast<uint64_t>(mc), static_cast<uint64_t>(k),
+                            static_cast<uint32_t>(plan.m_pad), &tmap_a);
+        if (rc != HFRK_SUCCESS) return rc;
+
+        GemmParams p;
+        p.d = static_cast<uint8_t*>(D) + static_cast<size_t>(m0) * n * out_elem;
+        p.scale = scale_dev;
+        p.kind_factor = (a_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f) * (w_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f);
+        p.m = mc;
+        p.n = n;
+        p.k = k;
+        p.m_pad = plan.m_pad;
+        p.num_kblocks = plan.num_kblocks;
+        p.split = plan.split;
+        p.stages = plan.stages;
+        p.d_dtype = d_dtype;
+        p.accumulate = accumulate ? 1 : 0;
+
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(static_cast<unsigned>((n + kTileN - 1) / kTileN), static_cast<unsigned>(plan.split), 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+        cfg.stream = stream;
+        cudaLaunchAttribute attrs[2];
+        unsigned num_attrs = 0;
+        if (plan.split > 1) {
+            attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
+            attrs[num_attrs].val.clusterDim.x = 1;
+            attrs[num_attrs].val.clusterDim.y = static_cast<unsigned>(plan.split);
+            attrs[num_attrs].val.clusterDim.z = 1;
+            ++num_attrs;
+        }
+        if (use_pdl) {
+            attrs[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+            ++num_attrs;
+        }
+        cfg.attrs = attrs;
+        cfg.numAttrs = num_attrs;
+        HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel, tmap_w, tmap_a, p));
+    }
+    return HFRK_SUCCESS;
+}
+
+}  // namespace
+}  // namespace hfrk
+
+// =============================================================================== C ABI
+
+extern "C" int hfrk_skinny_gemm_fp8(const void* A, const void* W, void* D, const float* scale_dev, int m, int n,
+                                    int k, int64_t w_row_stride, int a_kind, int w_kind, int d_dtype,
+                                    int accumulate, int split_k_hint, void* stream) {
+    if (split_k_hint < 0) return HFRK_INVALID_CONFIG;
+    if (split_k_hint > hfrk::kMaxSplit) split_k_hint = hfrk::kMaxSplit;
+    return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
+                             split_k_hint, 0, hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* scale_dev, int m, int n,
+                                       int k, int64_t w_row_stride, int a_kind, int w_kind, int d_dtype,
+                                       int accumulate, int split_k, int num_stages, int use_pdl, void* stream) {
+    return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate, split_k,
+                             num_stages, use_pdl, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t hfrk_host_call_workspace_bytes(int m, int n, int k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    const int64_t a_bytes = (static_cast<int64_t>(m) * k + 255) / 256 * 256;
+    const int64_t d_bytes = (static_cast<int64_t>(m) * n * 2 + 255) / 256 * 256;
+    return a_bytes + d_bytes;
+}
+
+extern "C" int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, void* D_host,
+                                         const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
+                                         int a_kind, int w_kind, int d_dtype, int accumulate, void* work_dev,
+                                         void* stream) {
+    if (A_host == nullptr || D_host == nullptr || work_dev == nullptr || m <= 0 || n <= 0 || k <= 0)
+        return HFRK_INVALID_CONFIG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t a_bytes = static_cast<size_t>(m) * k;
+    const size_t d_bytes = static_cast<size_t>(m) * n * 2;
+    uint8_t* a_dev = static_cast<uint8_t*>(work_dev);
+    uint8_t* d_dev = a_dev + (a_bytes + 255) / 256 * 256;
+    HFRK_CUDA_TRY(cudaMemcpyAsync(a_dev, A_host, a_bytes, cudaMemcpyHostToDevice, s));
+    if (accumulate) HFRK_CUDA_TRY(cudaMemcpyAsync(d_dev, D_host, d_bytes, cudaMemcpyHostToDevice, s));
+    int rc = hfrk::launch_gemm(a_dev, W_dev, d_dev, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype,
+                               accumulate, 0, 0, 0, s);
+    if (rc != HFRK_SUCCESS) return rc;
+    HFRK_CUDA_TRY(cudaMemcpyAsync(D_host, d_dev, d_bytes, cudaMemcpyDeviceToHost, s));
+    HFRK_CUDA_TRY(cudaStreamSynchronize(s));
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int split_k_hint, int* out6) {
+    if (out6 == nullptr) return HFRK_INVALID_CONFIG;
+    hfrk::Plan plan;
+    const int mc = m > hfrk::kMaxMPad ? hfrk::kMaxMPad : m;
+    int rc = hfrk::make_plan(mc, n, k, split_k_hint, 0, &plan);
+    if (rc != HFRK_SUCCESS) return rc;
+    out6[0] = plan.split;
+    out6[1] = plan.stages;
+    out6[2] = plan.ctas;
+    out6[3] = plan.smem_bytes;
+    out6[4] = plan.m_pad;
+    out6[5] = plan.num_kblocks;
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_device_status(int clear, unsigned int* word_out) {
+    unsigned int word = 0;
+    HFRK_CUDA_TRY(cudaMemcpyFromSymbol(&word, hfrk::g_device_status, sizeof(word)));
+    if (clear && word != 0) {
+        const unsigned int zero = 0;
+        HFRK_CUDA_TRY(cudaMemcpyToSymbol(hfrk::g_device_status, &zero, sizeof(zero)));
+    }
+    if (word_out != nullptr) *word_out = word;
+    return word == 0 ? HFRK_SUCCESS : HFRK_DEVICE_TIMEOUT;
+}

@@ -1,0 +1,149 @@
+"""ctypes view of ``libhfrk_b200.so``, the C ABI declared in ``include/hfrk_b200.h``.
+
+The torch op is a shim over the same library; this module lets benchmarks and tests reach the
+entry points that have no torch schema (pinned launch shapes, host-buffer calls, the plan query).
+There is no fallback: if the library is missing, importing this module raises.
+"""
+import ctypes
+import os
+from typing import Optional, Tuple
+
+import torch
+
+_LIB_NAME = "libhfrk_b200.so"
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+
+E4M3FN, E4M3FNUZ = 0, 1
+F16, BF16 = 0, 1
+
+STATUS_NAMES = {
+    0: "SUCCESS", 1: "M_ABOVE_WARPTILE_M", 2: "N_NOT_EVEN", 3: "K_NOT_DIVISIBLE", 4: "TOO_MANY_WARPS",
+    5: "QSIZE_TOO_SMALL", 6: "INVALID_CONFIG", 7: "BAD_ALIGNMENT", 8: "BAD_DTYPE", 9: "CUDA_ERROR",
+    10: "DEVICE_TIMEOUT", 11: "BAD_WORLD", 12: "TOO_LARGE",
+}
+
+# Every symbol the header declares; tests check that the built library exports all of them.
+EXPORTED_SYMBOLS = (
+    "hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
+    "hfrk_host_call_workspace_bytes", "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan",
+    "hfrk_device_status", "hfrk_last_error", "hfrk_version",
+)
+
+
+def library_path() -> str:
+    return os.path.join(_PKG_DIR, _LIB_NAME)
+
+
+def _load() -> ctypes.CDLL:
+    path = library_path()
+    if not os.path.exists(path):
+        raise ImportError(
+            f"{path} is missing: build it with `python hf-rocm-kernels_b200/build.py` "
+            "(nvcc, sm_100a). This package has no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(path)
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    common = [vp, vp, vp, vp, i32, i32, i32, i64, i32, i32, i32, i32]
+    lib.hfrk_skinny_gemm_fp8.argtypes = common + [i32, vp]
+    lib.hfrk_skinny_gemm_fp8_ex.argtypes = common + [i32, i32, i32, vp]
+    lib.hfrk_skinny_gemm_fp8_host.argtypes = common + [vp, vp]
+    lib.hfrk_skinny_gemm_fp8_simt.argtypes = common + [vp]
+    lib.hfrk_host_call_workspace_bytes.argtypes = [i32, i32, i32]
+    lib.hfrk_host_call_workspace_bytes.restype = i64
+    lib.hfrk_skinny_gemm_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32)]
+    lib.hfrk_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_uint)]
+    lib.hfrk_last_error.restype = ctypes.c_char_p
+    for name in ("hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
+                 "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan", "hfrk_device_status", "hfrk_version"):
+        getattr(lib, name).restype = i32
+    return lib
+
+
+lib = _load()
+
+
+class HfrkError(RuntimeError):
+    def __init__(self, code: int):
+        self.code = code
+        detail = lib.hfrk_last_error().decode() if code == 9 else ""
+        super().__init__(f"hfrk status {code} ({STATUS_NAMES.get(code, '?')}) {detail}".strip())
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise HfrkError(code)
+
+
+def fp8_kind(dtype: torch.dtype) -> int:
+    if dtype == torch.float8_e4m3fn:
+        return E4M3FN
+    if dtype == torch.float8_e4m3fnuz:
+        return E4M3FNUZ
+    raise TypeError(f"expected float8_e4m3fn or float8_e4m3fnuz, got {dtype}")
+
+
+def out_kind(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return F16
+    if dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"expected float16 or bfloat16 output, got {dtype}")
+
+
+def _common_args(a: torch.Tensor, w: torch.Tensor, d: torch.Tensor, scale: torch.Tensor, accumulate: bool):
+    """(A[M,K], W[N,K] with unit inner stride, D[M,N], scale[1]) -> the leading C arguments."""
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and w.stride(1) == 1 and a.is_contiguous() and d.is_contiguous()
+    assert tuple(d.shape) == (m, n) and scale.numel() == 1 and scale.dtype == torch.float32
+    return (a.data_ptr(), w.data_ptr(), d.data_ptr(), scale.data_ptr(), m, n, k, w.stride(0),
+            fp8_kind(a.dtype), fp8_kind(w.dtype), out_kind(d.dtype), int(accumulate))
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream], device: torch.device) -> int:
+    return (stream or torch.cuda.current_stream(device)).cuda_stream
+
+
+def skinny_gemm(a, w, d, scale, accumulate=True, split_k_hint=0, stream=None) -> int:
+    """``hfrk_skinny_gemm_fp8`` on torch CUDA tensors; ``w`` is the [N,K] weight (rows may be padded)."""
+    with torch.cuda.device(a.device):
+        return lib.hfrk_skinny_gemm_fp8(*_common_args(a, w, d, scale, accumulate), split_k_hint,
+                                        _stream_ptr(stream, a.device))
+
+
+def skinny_gemm_ex(a, w, d, scale, accumulate=True, split_k=0, num_stages=0, use_pdl=False, stream=None) -> int:
+    with torch.cuda.device(a.device):
+        return lib.hfrk_skinny_gemm_fp8_ex(*_common_args(a, w, d, scale, accumulate), split_k, num_stages,
+                                           int(use_pdl), _stream_ptr(stream, a.device))
+
+
+def skinny_gemm_simt(a, w, d, scale, accumulate=True, stream=None) -> int:
+    with torch.cuda.device(a.device):
+        return lib.hfrk_skinny_gemm_fp8_simt(*_common_args(a, w, d, scale, accumulate),
+                                             _stream_ptr(stream, a.device))
+
+
+def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True, stream=None) -> int:
+    """Host-buffer call: ``a_host``/``d_host`` are (pinned) CPU tensors, weights and scale stay on the GPU."""
+    m, k = a_host.shape
+    n = w_dev.shape[0]
+    assert a_host.device.type == "cpu" and d_host.device.type == "cpu" and w_dev.stride(1) == 1
+    assert work_dev.numel() * work_dev.element_size() >= lib.hfrk_host_call_workspace_bytes(m, n, k)
+    with torch.cuda.device(w_dev.device):
+        return lib.hfrk_skinny_gemm_fp8_host(
+            a_host.data_ptr(), w_dev.data_ptr(), d_host.data_ptr(), scale_dev.data_ptr(), m, n, k, w_dev.stride(0),
+            fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype), out_kind(d_host.dtype), int(accumulate),
+            work_dev.data_ptr(), _stream_ptr(stream, w_dev.device))
+
+
+def plan(m: int, n: int, k: int, split_k_hint: int = 0) -> dict:
+    out = (ctypes.c_int * 6)()
+    check(lib.hfrk_skinny_gemm_plan(m, n, k, split_k_hint, out))
+    keys = ("split_k", "num_stages", "ctas", "smem_bytes", "m_pad", "k_blocks")
+    return dict(zip(keys, list(out)))
+
+
+def device_status(clear: bool = True) -> Tuple[int, int]:
+    word = ctypes.c_uint(0)
+    code = lib.hfrk_device_status(int(clear), ctypes.byref(word))
+    return code, word.value

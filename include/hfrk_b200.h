@@ -1,0 +1,117 @@
+/*
+ * hfrk_b200.h - C ABI of the B200 (sm_100a) FP8 skinny GEMM library, libhfrk_b200.so.
+ *
+ * One operation:   D[m,n] <- (accumulate ? D_in[m,n] : 0) + scale * sum_k A[m,k] * W[n,k]
+ *   A  [M,K]  fp8 e4m3, row-major, contiguous
+ *   W  [N,K]  fp8 e4m3, row-major with a row stride of w_row_stride elements
+ *   D  [M,N]  fp16 or bf16, row-major, contiguous, updated in place
+ *   scale     one fp32 value read ON THE DEVICE (the product scale_a * scale_w)
+ *
+ * Every pointer is a plain device pointer unless the name says "host". Nothing here takes or
+ * returns a torch type; the torch op `_HFRK_C::skinny_gemm_tb` is a thin shim over these calls.
+ *
+ * The entry points stand where the reference (huggingface/hf-rocm-kernels) has
+ *   csrc/op_src/skinny_gemm/skinny_gemm_binding.cu:16-42   (tensor -> pointers, shapes, stream)
+ *   csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:21-71    (validation, grid/block, dispatch)
+ *   csrc/op_src/skinny_gemm/skinny_gemm_kernel.cu:6-79     (the device kernel)
+ * and keep its convention of returning a status int instead of throwing
+ * (csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:9-17).
+ */
+#ifndef HFRK_B200_H_
+#define HFRK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------
+ * 0..6 are the reference's SkinnyGemmReturnCode values (skinny_gemm_caller.cu:9-17); the B200
+ * kernel never needs 1, 2, 4, 5 (no warp-tile, lane or queue knobs) but keeps the numbering so
+ * that callers that log the code read the same meaning. Codes >= 7 are new. */
+enum hfrk_status {
+    HFRK_SUCCESS = 0,
+    HFRK_M_ABOVE_WARPTILE_M = 1,        /* never returned */
+    HFRK_N_NOT_EVEN = 2,                /* never returned: odd N is handled */
+    HFRK_K_NOT_DIVISIBLE = 3,           /* K must be a multiple of 16 (TMA row pitch) */
+    HFRK_TOO_MANY_WARPS = 4,            /* never returned */
+    HFRK_QSIZE_TOO_SMALL = 5,           /* never returned */
+    HFRK_INVALID_CONFIG = 6,            /* m, n, k <= 0, or a tuning value out of range */
+    HFRK_BAD_ALIGNMENT = 7,             /* base pointer or W row stride not 16-byte aligned */
+    HFRK_BAD_DTYPE = 8,                 /* unknown fp8 kind or output dtype */
+    HFRK_CUDA_ERROR = 9,                /* a CUDA runtime/driver call failed (see hfrk_last_error) */
+    HFRK_DEVICE_TIMEOUT = 10,           /* a bounded device-side wait ran out (pipeline or peer) */
+    HFRK_BAD_WORLD = 11,                /* row-parallel: rank/world/peer table inconsistent */
+    HFRK_TOO_LARGE = 12                 /* a size exceeds a documented fixed capacity */
+};
+
+/* fp8 encodings. E4M3FNUZ operands are reinterpreted bit-for-bit as E4M3FN and the result is
+ * multiplied by 0.5 per FNUZ operand on the device: for every bit pattern the reference's
+ * quantiser can emit (hf_rocm_kernels/utils/fp8.py:17-29) value_fnuz == value_fn / 2 exactly. */
+enum hfrk_fp8_kind { HFRK_E4M3FN = 0, HFRK_E4M3FNUZ = 1 };
+enum hfrk_out_dtype { HFRK_F16 = 0, HFRK_BF16 = 1 };
+
+/* Single-GPU skinny GEMM on `stream` (a cudaStream_t passed as void*), asynchronous, no host
+ * synchronisation, no allocation: capturable in a CUDA graph.
+ * Replaces skinny_gemm_tb / skinny_gemm() of the reference
+ * (csrc/op_src/skinny_gemm/skinny_gemm_binding.cu:16-42, skinny_gemm_caller.cu:21-71).
+ *   a_kind, w_kind : enum hfrk_fp8_kind       d_dtype : enum hfrk_out_dtype
+ *   accumulate     : 1 = D += result (the reference's contract, wrapped.py:115), 0 = overwrite
+ *   split_k_hint   : 0 = choose automatically; >= 1 = requested K split (clamped to what the
+ *                    launch supports). The reference's split_k argument maps here. */
+int hfrk_skinny_gemm_fp8(const void* A, const void* W, void* D, const float* scale_dev,
+                         int m, int n, int k, int64_t w_row_stride,
+                         int a_kind, int w_kind, int d_dtype, int accumulate,
+                         int split_k_hint, void* stream);
+
+/* Same operation with the launch shape pinned by the caller (benchmark sweeps, tuning):
+ *   split_k    : 0 = automatic, else 1..16        num_stages : 0 = automatic, else 2..12
+ *   use_pdl    : 1 = launch with programmatic stream serialisation so the weight stream of this
+ *                call may start while the previous kernel on the stream drains.
+ * Takes the place of the reference's nine tuning ints
+ * (csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:28-32). */
+int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* scale_dev,
+                            int m, int n, int k, int64_t w_row_stride,
+                            int a_kind, int w_kind, int d_dtype, int accumulate,
+                            int split_k, int num_stages, int use_pdl, void* stream);
+
+/* Host-buffer form of the same call, for callers whose activations live in host memory:
+ * copies A (and D when accumulate=1) host->device, runs the GEMM against the device-resident
+ * weights W_dev, copies D back, and synchronises `stream`. `work_dev` is caller-owned device
+ * scratch of at least hfrk_host_call_workspace_bytes(m, n, k) bytes. Weights stay on the
+ * device: they are model state, as in the reference where they are torch CUDA tensors
+ * (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:28-35). */
+int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, void* D_host,
+                              const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
+                              int a_kind, int w_kind, int d_dtype, int accumulate,
+                              void* work_dev, void* stream);
+int64_t hfrk_host_call_workspace_bytes(int m, int n, int k);
+
+/* Plain SIMT (no TMA, no tensor core) kernel for the same operation. It exists to bisect faults
+ * in the tensor-core path and as an on-device cross-check at sizes where a CPU check is slow.
+ * It is never selected by hfrk_skinny_gemm_fp8. No counterpart in the reference. */
+int hfrk_skinny_gemm_fp8_simt(const void* A, const void* W, void* D, const float* scale_dev,
+                              int m, int n, int k, int64_t w_row_stride,
+                              int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);
+
+/* Launch shape the automatic heuristic would pick (for logs and tests; no GPU work).
+ * out[0]=split_k, out[1]=num_stages, out[2]=grid CTAs, out[3]=dynamic shared memory bytes,
+ * out[4]=padded token count (MMA N), out[5]=K blocks of 128. Returns a status code. */
+int hfrk_skinny_gemm_plan(int m, int n, int k, int split_k_hint, int* out6);
+
+/* Device-side status word of the current device: 0, or the HFRK_DEVICE_TIMEOUT details packed
+ * as (code << 24 | role << 16 | block index & 0xffff). Reads it with a synchronous copy, and
+ * clears it when `clear` is non-zero. Kernels only ever write it when a bounded wait runs out. */
+int hfrk_device_status(int clear, unsigned int* word_out);
+
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* hfrk_last_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int hfrk_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HFRK_B200_H_ */
