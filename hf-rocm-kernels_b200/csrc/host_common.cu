@@ -16,7 +16,7 @@ void set_last_error(const char* text) { g_last_error = text ? text : ""; }
 int default_use_pdl() {
     static const int value = [] {
         const char* env = std::getenv("HFRK_PDL");
-        return (env != nullptr && std::strcmp(env, "1") == 0) ? 1 : 0;
+        return (env != nullptr && std::strcmp(env, "0") == 0) ? 0 : 1;
     }();
     return value;
 }

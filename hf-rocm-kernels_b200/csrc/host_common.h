@@ -12,8 +12,10 @@ namespace hfrk {
 
 void set_last_error(const char* text);
 
-// 1 when the environment asks for programmatic dependent launch on the plain entry point
-// (HFRK_PDL=1). Off by default: it is only safe when nothing earlier on the stream writes W.
+// 1 unless the environment switches programmatic dependent launch off for the plain entry points
+// (HFRK_PDL=0). With it the weight stream of a call starts while the previous kernel on the stream
+// drains, which is only correct when that kernel does not write W: true for inference, where
+// weights are static.
 int default_use_pdl();
 
 }  // namespace hfrk

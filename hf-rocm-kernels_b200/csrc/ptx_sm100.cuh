@@ -169,6 +169,13 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Execution-only cluster barrier: orders nothing in memory. Enough to keep a CTA alive until its
+// peers have finished reading its shared memory (their loads have returned before they arrive).
+__device__ __forceinline__ void cluster_sync_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t dsmem_map(uint32_t local_smem, uint32_t cta_rank) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(cta_rank));

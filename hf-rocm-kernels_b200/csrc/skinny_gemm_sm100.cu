@@ -38,25 +38,10 @@
 #include "../../include/hfrk_b200.h"
 #include "host_common.h"
 #include "ptx_sm100.cuh"
+#include "skinny_gemm_common.cuh"
+#include "skinny_gemm_streamk.cuh"
 
 namespace hfrk {
-
-constexpr int kTileN = 128;                        // W rows per CTA  (tcgen05.mma M)
-constexpr int kBlockK = 128;                       // fp8 elements per stage row = one swizzle atom
-constexpr int kUmmaK = 32;                         // K of one tcgen05.mma for 8-bit operands
-constexpr int kWStageBytes = kTileN * kBlockK;     // 16 KiB of W per stage
-constexpr int kMaxStages = 12;
-constexpr int kThreads = 192;                      // 4 epilogue warps + producer warp + MMA warp
-constexpr int kEpilogueThreads = 128;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kMaxMPad = 64;                       // tokens per launch (larger M loops on the host)
-constexpr int kMaxSplit = 16;
-constexpr int kSmemLimit = 227 * 1024;
-constexpr int kNumSms = 148;
-constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds of SM clock
-
-enum Role : int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3 };
 
 struct Ctrl {
     uint64_t full[kMaxStages];    // TMA -> MMA : stage holds data
@@ -65,7 +50,6 @@ struct Ctrl {
     uint32_t tmem_base;
     volatile uint32_t abort;      // set by the first role whose wait ran out
 };
-constexpr int kCtrlBytes = 256;
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
 
 struct GemmParams {
@@ -79,52 +63,16 @@ struct GemmParams {
     int stages;
     int d_dtype;
     int accumulate;
+    unsigned long long* stamps;  // optional [cta][8] globaltimer samples (diagnostic entry point only)
 };
 
-// Device-side status of this library on the current device. Written only when a bounded wait
-// runs out; read and cleared by hfrk_device_status().
-__device__ unsigned int g_device_status = 0;
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
 
-__device__ __forceinline__ void record_timeout(int role) {
-    const unsigned int word = (static_cast<unsigned int>(HFRK_DEVICE_TIMEOUT) << 24) |
-                              (static_cast<unsigned int>(role) << 16) | (blockIdx.x & 0xffffu);
-    atomicCAS(&g_device_status, 0u, word);
-}
-
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                            int role) {
-    const long long start = clock64();
-    for (;;) {
-        for (int i = 0; i < 32; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
-        }
-        if (*abort_flag) return false;
-        if (clock64() - start > kWaitLimitCycles) {
-            *abort_flag = 1u;
-            record_timeout(role);
-            return false;
-        }
-    }
-}
-
-// Waits for the phase with the given parity to complete; false if the wait ran out or another
-// role of this CTA already gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                  int role) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, role);
-}
-
-__device__ __forceinline__ float load_out(const void* d, size_t idx, int dtype) {
-    return dtype == HFRK_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(d)[idx])
-                              : __half2float(static_cast<const __half*>(d)[idx]);
-}
-
-__device__ __forceinline__ void store_out(void* d, size_t idx, int dtype, float v) {
-    if (dtype == HFRK_BF16) {
-        static_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
-    } else {
-        static_cast<__half*>(d)[idx] = __float2half_rn(v);
+__device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
+    if (p.stamps != nullptr) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.stamps[(static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
     }
 }
 
@@ -146,6 +94,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kTileN;
+    if (threadIdx.x == 0) stamp(p, 0);
 
     // K blocks of this CTA: a contiguous range, the remainder spread over the first ranks.
     const int rank = p.split > 1 ? static_cast<int>(cluster_cta_rank()) : 0;
@@ -158,10 +107,10 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const uint32_t tmem_cols = p.m_pad <= 32 ? 32u : 64u;
     uint64_t pol_w = 0, pol_a = 0;
 
+    // Set-up: the producer initialises the barriers, signals the other warps through a named
+    // barrier it only arrives at, and goes straight on to the first loads.
     if (warp == kProducerWarp) {
         if (lane == 0) {
-            prefetch_tensormap(&tmap_w);
-            prefetch_tensormap(&tmap_a);
             ctrl->abort = 0u;
             for (int s = 0; s < p.stages; ++s) {
                 mbar_init(full_bar + 8u * s, 1);
@@ -169,6 +118,12 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
             mbar_init(accum_bar, 1);
             mbar_init_fence();
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 2, %0;" ::"r"(kThreads) : "memory");
+        if (lane == 0) {
+            prefetch_tensormap(&tmap_w);
+            prefetch_tensormap(&tmap_a);
             pol_w = l2_policy_evict_first();
             pol_a = l2_policy_evict_last();
             // Start the weight stream before anything else in the CTA is ready: W does not depend
@@ -183,17 +138,21 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 tma_load_2d(ring_addr + i * stage_bytes + kWStageBytes, &tmap_a, full_bar + 8u * i,
                             (kb_start + i) * kBlockK, 0, pol_a);
             }
+            stamp(p, 2);
         }
         __syncwarp();
-    } else if (warp == kMmaWarp) {
-        tmem_alloc(smem_u32(&ctrl->tmem_base), tmem_cols);
-        tmem_relinquish_alloc_permit();
+    } else {
+        if (warp == kMmaWarp) {
+            tmem_alloc(smem_u32(&ctrl->tmem_base), tmem_cols);
+            tmem_relinquish_alloc_permit();
+            tcgen05_fence_before_sync();
+        }
+        asm volatile("bar.sync 2, %0;" ::"r"(kThreads) : "memory");
+        tcgen05_fence_after_sync();
     }
-    tcgen05_fence_before_sync();
-    __syncthreads();
-    tcgen05_fence_after_sync();
     pdl_launch_dependents();
     const uint32_t tmem_acc = ctrl->tmem_base;
+    if (threadIdx.x == 0) stamp(p, 1);
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
@@ -231,6 +190,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const int s = i % p.stages;
                 const uint32_t round = static_cast<uint32_t>(i / p.stages);
                 if (!mbar_wait_bounded(full_bar + 8u * s, round & 1u, &ctrl->abort, kRoleMma)) break;
+                if (i == 0) stamp(p, 3);
                 tcgen05_fence_after_sync();
                 const uint64_t w_desc = umma_desc_kmajor_sw128(ring_addr + s * stage_bytes);
                 const uint64_t a_desc = umma_desc_kmajor_sw128(ring_addr + s * stage_bytes + kWStageBytes);
@@ -242,6 +202,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 umma_commit(empty_bar + 8u * s);
             }
             umma_commit(accum_bar);
+            stamp(p, 4);
         }
         __syncwarp();
     } else {
@@ -264,6 +225,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         bool ok = mbar_wait_bounded(accum_bar, 0u, &ctrl->abort, kRoleEpilogue);
         ok = __all_sync(0xffffffffu, ok) && ctrl->abort == 0u;
         ok = __all_sync(0xffffffffu, ok);
+        if (threadIdx.x == 0) stamp(p, 5);
         tcgen05_fence_after_sync();
         if (ok) {
             float* const partial = reinterpret_cast<float*>(ring_ptr);
@@ -295,33 +257,73 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         // Reduce-scatter of the split-K partial tiles through distributed shared memory: CTA `rank`
         // finalises elements [rank*chunk, (rank+1)*chunk) of the m x 128 tile, reading every peer's
         // copy (its own included) in rank order.
+        constexpr int kPrefetch = 8;
+        const int total = p.m * kTileN;
+        const int chunk = (total + p.split - 1) / p.split;
+        const int e_begin = rank * chunk;
+        const int e_end = e_begin + chunk < total ? e_begin + chunk : total;
+        const bool reducer = warp < kEpilogueThreads / 32;
+        // Nothing may be outstanding in global memory here: the release half of the barrier would
+        // wait for it. D_in is therefore requested after the barrier, together with the peers' data.
         cluster_sync_all();
-        if (warp < kEpilogueThreads / 32 && ctrl->abort == 0u) {
+        float d_in[kPrefetch];
+        if (reducer) {
+#pragma unroll
+            for (int it = 0; it < kPrefetch; ++it) {
+                const int e = e_begin + static_cast<int>(threadIdx.x) + it * kEpilogueThreads;
+                const int n = n0 + (e % kTileN);
+                d_in[it] = (p.accumulate && e < e_end && n < p.n)
+                               ? load_out(p.d, static_cast<size_t>(e / kTileN) * p.n + n, p.d_dtype)
+                               : 0.0f;
+            }
+        }
+        if (reducer && ctrl->abort == 0u) {
             const float scale = __ldg(p.scale) * p.kind_factor;
-            const int total = p.m * kTileN;
-            const int chunk = (total + p.split - 1) / p.split;
-            const int e_begin = rank * chunk;
-            const int e_end = e_begin + chunk < total ? e_begin + chunk : total;
-            for (int e = e_begin + static_cast<int>(threadIdx.x); e < e_end; e += kEpilogueThreads) {
+#pragma unroll
+            for (int it = 0; it < kPrefetch; ++it) {
+                const int e = e_begin + static_cast<int>(threadIdx.x) + it * kEpilogueThreads;
+                if (e < e_end) {
+                    // All peers' values are requested before the first one is consumed.
+                    float v[kMaxSplit];
+#pragma unroll
+                    for (int q = 0; q < kMaxSplit; ++q) {
+                        v[q] = q < p.split ? dsmem_ld_f32(dsmem_map(ring_addr + 4u * static_cast<uint32_t>(e),
+                                                                    static_cast<uint32_t>(q)))
+                                           : 0.0f;
+                    }
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < kMaxSplit; ++q) sum += v[q];
+                    const int n = n0 + (e % kTileN);
+                    if (n < p.n) {
+                        store_out(p.d, static_cast<size_t>(e / kTileN) * p.n + n, p.d_dtype,
+                                  fmaf(sum, scale, d_in[it]));
+                    }
+                }
+            }
+            // Token counts above 16 leave more than kPrefetch elements per thread for small splits.
+            for (int e = e_begin + static_cast<int>(threadIdx.x) + kPrefetch * kEpilogueThreads; e < e_end;
+                 e += kEpilogueThreads) {
                 float sum = 0.0f;
                 for (int q = 0; q < p.split; ++q) {
                     sum += dsmem_ld_f32(dsmem_map(ring_addr + 4u * static_cast<uint32_t>(e), static_cast<uint32_t>(q)));
                 }
-                const int m = e / kTileN;
                 const int n = n0 + (e % kTileN);
                 if (n < p.n) {
-                    const size_t idx = static_cast<size_t>(m) * p.n + n;
-                    const float d_in = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
-                    store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d_in));
+                    const size_t idx = static_cast<size_t>(e / kTileN) * p.n + n;
+                    const float d0 = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
+                    store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d0));
                 }
             }
         }
-        cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
+        cluster_sync_relaxed();  // no CTA leaves while a peer may still read its shared memory
     }
 
+    if (threadIdx.x == 0) stamp(p, 6);
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kMmaWarp) tmem_dealloc(tmem_acc, tmem_cols);
+    if (threadIdx.x == 0) stamp(p, 7);
 }
 
 // =============================================================================== host side
@@ -415,12 +417,13 @@ struct Plan {
 
 int round_up(int v, int to) { return (v + to - 1) / to * to; }
 
-// Launch shape for one launch of m <= kMaxMPad tokens.
-//   split  : enough K splits that tiles * split covers the SMs, never leaving a split fewer than
-//            four K blocks (a split that short is all pipeline fill).
-//   stages : when the grid fits one CTA per SM the ring takes all of shared memory (12 stages at
-//            m_pad 16), which also keeps the CTAs of a cluster on different SMs; larger grids use
-//            half of it so two CTAs share an SM and one's epilogue overlaps the other's stream.
+// Launch shape of the cluster kernel for one launch of m <= kMaxMPad tokens, from sweeps on B200
+// (148 SMs) over the Llama-3 8B/70B projection shapes:
+//   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream; with fewer
+//     tiles than SMs the K split is chosen so that tiles * split comes to about two CTAs per SM;
+//   * short rings and many CTAs beat long rings and few: three co-resident CTAs of four 18 KiB
+//     stages hide each other's fill, drain and reduction better than one CTA with twelve stages;
+//   * a split never gets fewer than four K blocks (it would be all pipeline fill).
 int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
     if (split_req < 0 || split_req > kMaxSplit || stages_req < 0 || stages_req == 1 || stages_req > kMaxStages)
@@ -434,29 +437,23 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     int split = split_req;
     if (split == 0) {
         split = 1;
-        const int by_depth = nkb / 4 > 1 ? nkb / 4 : 1;
-        while (split < 8 && split < by_depth && tiles * split < 128) ++split;
+        if (tiles < kNumSms) {
+            split = (2 * kNumSms + tiles / 2) / tiles;
+            if (split > 8) split = 8;
+            while (split > 1 && nkb / split < 4) --split;
+        }
     }
     if (split > nkb) split = nkb;
 
-    const int ctas = tiles * split;
-    int stages = stages_req;
-    const bool one_per_sm = ctas <= kNumSms;
-    if (stages == 0) {
-        stages = one_per_sm ? max_stages_fit : (kSmemLimit / 2 - 1024 - 1024 - kCtrlBytes) / stage_bytes;
-    }
+    int stages = stages_req != 0 ? stages_req : (split > 1 ? 4 : 6);
     if (stages > max_stages_fit) stages = max_stages_fit;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return HFRK_INVALID_CONFIG;
 
-    int smem = 1024 + stages * stage_bytes + kCtrlBytes;
-    // Fewer stages than half of shared memory would let several CTAs of one cluster pile onto one
-    // SM while others idle; keep the footprint above half when the grid is at most one wave.
-    if (one_per_sm && smem <= kSmemLimit / 2) smem = kSmemLimit / 2 + 1024;
     plan->split = split;
     plan->stages = stages;
-    plan->ctas = ctas;
-    plan->smem_bytes = smem;
+    plan->ctas = tiles * split;
+    plan->smem_bytes = 1024 + stages * stage_bytes + kCtrlBytes;
     plan->m_pad = m_pad;
     plan->num_kblocks = nkb;
     return HFRK_SUCCESS;
@@ -472,6 +469,10 @@ int prepare_device_once() {
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<1>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<2>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     if (dev >= 0 && dev < 64) done[dev] = true;
     return HFRK_SUCCESS;
 }
@@ -491,13 +492,181 @@ int validate(const void* A, const void* W, void* D, const float* scale_dev, int 
     return HFRK_SUCCESS;
 }
 
+// ---------------------------------------------------------------- stream-K scratch
+// The stream-K kernel needs fp32 scratch for partial tiles and one counter per tile. The library
+// owns it: kScratchLanes independent sets per device, allocated together on the first call on
+// that device (which therefore must not happen inside a stream capture). A stream is bound to a
+// lane the first time it is seen; calls on one stream are ordered, so they can share a lane, and
+// up to kScratchLanes streams can run GEMMs concurrently without touching each other's scratch.
+constexpr int kScratchLanes = 4;
+constexpr int kSkMaxGrid = 2 * kNumSms;
+constexpr int kSkMaxTiles = 65536;
+constexpr size_t kLanePartialFloats = static_cast<size_t>(2) * kSkMaxGrid * kMaxMPad * kTileN;
+
+struct DeviceScratch {
+    bool ready = false;
+    float* partials[kScratchLanes] = {};
+    unsigned int* counters[kScratchLanes] = {};
+    std::unordered_map<cudaStream_t, int> lane_of;
+    int next_lane = 0;
+};
+std::mutex g_scratch_mutex;
+DeviceScratch g_scratch[64];
+
+int scratch_for(cudaStream_t stream, float** partials, unsigned int** counters) {
+    int dev = 0;
+    HFRK_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return HFRK_INVALID_CONFIG;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    DeviceScratch& sc = g_scratch[dev];
+    if (!sc.ready) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        HFRK_CUDA_TRY(cudaStreamIsCapturing(stream, &capturing));
+        if (capturing != cudaStreamCaptureStatusNone) {
+            set_last_error("first call on this device happened inside a stream capture: call the GEMM once "
+                           "outside the capture so that its scratch memory can be allocated");
+            return HFRK_CUDA_ERROR;
+        }
+        const size_t lane_bytes = kLanePartialFloats * sizeof(float);
+        const size_t counter_bytes = static_cast<size_t>(kSkMaxTiles) * sizeof(unsigned int);
+        uint8_t* block = nullptr;
+        HFRK_CUDA_TRY(cudaMalloc(&block, kScratchLanes * (lane_bytes + counter_bytes)));
+        HFRK_CUDA_TRY(cudaMemset(block, 0, kScratchLanes * (lane_bytes + counter_bytes)));
+        for (int l = 0; l < kScratchLanes; ++l) {
+            sc.partials[l] = reinterpret_cast<float*>(block + l * lane_bytes);
+            sc.counters[l] = reinterpret_cast<unsigned int*>(block + kScratchLanes * lane_bytes + l * counter_bytes);
+        }
+        sc.ready = true;
+    }
+    auto it = sc.lane_of.find(stream);
+    int lane;
+    if (it == sc.lane_of.end()) {
+        lane = sc.next_lane++ % kScratchLanes;
+        if (sc.lane_of.size() > 1024) sc.lane_of.clear();
+        sc.lane_of.emplace(stream, lane);
+    } else {
+        lane = it->second;
+    }
+    *partials = sc.partials[lane];
+    *counters = sc.counters[lane];
+    return HFRK_SUCCESS;
+}
+
+struct SkPlan {
+    int grid, stages, units_per_stage, smem_bytes, m_pad, nkb, tiles;
+};
+
+// Stream-K launch shape: the grid covers the SMs `ctas_per_sm` times (never more CTAs than work
+// items), and each CTA's ring takes its share of the SM's shared memory.
+int make_sk_plan(int m, int n, int k, int ctas_per_sm, int stages_req, SkPlan* plan) {
+    if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
+    if (ctas_per_sm < 0 || ctas_per_sm > 2 || stages_req < 0 || stages_req == 1 || stages_req > kSkMaxStages)
+        return HFRK_INVALID_CONFIG;
+    const int m_pad = round_up(m, 16);
+    const int tiles = (n + kTileN - 1) / kTileN;
+    const int nkb = (k + kBlockK - 1) / kBlockK;
+    if (tiles > kSkMaxTiles) return HFRK_TOO_LARGE;
+    const long long units = static_cast<long long>(tiles) * nkb;
+    if (units > 0x3fffffff) return HFRK_TOO_LARGE;
+    if (ctas_per_sm == 0) ctas_per_sm = 2;
+    // Two CTAs per SM have two MMA-issuing threads, so single-K-block stages (more of them in
+    // flight) win; a lone CTA per SM needs the cheaper two-block stages to keep up.
+    const int ups = ctas_per_sm == 1 ? 2 : 1;
+    const int stage_bytes = ups * (kWStageBytes + m_pad * kBlockK);
+    const int budget = (228 * 1024 - ctas_per_sm * 1024) / ctas_per_sm;
+    int stages = stages_req != 0 ? stages_req : (budget - 1024 - kCtrlBytes) / stage_bytes;
+    if (stages > kSkMaxStages) stages = kSkMaxStages;
+    while (stages > 2 && 1024 + stages * stage_bytes + kCtrlBytes > kSmemLimit) --stages;
+    if (stages < 2 || 1024 + stages * stage_bytes + kCtrlBytes > kSmemLimit) return HFRK_INVALID_CONFIG;
+    long long grid = static_cast<long long>(kNumSms) * ctas_per_sm;
+    if (grid > units) grid = units;
+    plan->grid = static_cast<int>(grid);
+    plan->stages = stages;
+    plan->units_per_stage = ups;
+    plan->smem_bytes = 1024 + stages * stage_bytes + kCtrlBytes;
+    plan->m_pad = m_pad;
+    plan->nkb = nkb;
+    plan->tiles = tiles;
+    return HFRK_SUCCESS;
+}
+
+int launch_streamk(const void* A, const void* W, void* D, const float* scale_dev, int m, int n, int k,
+                   int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int ctas_per_sm,
+                   int stages_req, int use_pdl, cudaStream_t stream, unsigned long long* stamps) {
+    CUtensorMap tmap_w;
+    int rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                            static_cast<uint64_t>(w_row_stride), kTileN, &tmap_w);
+    if (rc != HFRK_SUCCESS) return rc;
+    float* partials = nullptr;
+    unsigned int* counters = nullptr;
+    rc = scratch_for(stream, &partials, &counters);
+    if (rc != HFRK_SUCCESS) return rc;
+
+    for (int m0 = 0; m0 < m; m0 += kMaxMPad) {
+        const int mc = m - m0 < kMaxMPad ? m - m0 : kMaxMPad;
+        SkPlan plan;
+        rc = make_sk_plan(mc, n, k, ctas_per_sm, stages_req, &plan);
+        if (rc != HFRK_SUCCESS) return rc;
+        const uint8_t* a_chunk = static_cast<const uint8_t*>(A) + static_cast<size_t>(m0) * k;
+        CUtensorMap tmap_a;
+        rc = get_tensor_map(a_chunk, static_cast<uint64_t>(k), static_cast<uint64_t>(mc), static_cast<uint64_t>(k),
+                            static_cast<uint32_t>(plan.m_pad), &tmap_a);
+        if (rc != HFRK_SUCCESS) return rc;
+
+        SkParams p;
+        p.d = static_cast<uint8_t*>(D) + static_cast<size_t>(m0) * n * 2;
+        p.scale = scale_dev;
+        p.kind_factor = (a_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f) * (w_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f);
+        p.m = mc;
+        p.n = n;
+        p.m_pad = plan.m_pad;
+        p.nkb = plan.nkb;
+        p.total_units = plan.tiles * plan.nkb;
+        p.stages = plan.stages;
+        p.d_dtype = d_dtype;
+        p.accumulate = accumulate ? 1 : 0;
+        p.partials = partials;
+        p.counters = counters;
+        p.stamps = stamps;
+
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(static_cast<unsigned>(plan.grid), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+        cfg.stream = stream;
+        cudaLaunchAttribute attrs[1];
+        unsigned num_attrs = 0;
+        if (use_pdl) {
+            attrs[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+            ++num_attrs;
+        }
+        cfg.attrs = attrs;
+        cfg.numAttrs = num_attrs;
+        if (plan.units_per_stage == 1) {
+            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_streamk_kernel<1>, tmap_w, tmap_a, p));
+        } else {
+            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_streamk_kernel<2>, tmap_w, tmap_a, p));
+        }
+    }
+    return HFRK_SUCCESS;
+}
+
 int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, int m, int n, int k,
-                int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int split_req,
-                int stages_req, int use_pdl, cudaStream_t stream) {
+                int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int variant,
+                int split_req, int ctas_per_sm, int stages_req, int use_pdl, cudaStream_t stream,
+                unsigned long long* stamps = nullptr) {
     int rc = validate(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype);
     if (rc != HFRK_SUCCESS) return rc;
     rc = prepare_device_once();
     if (rc != HFRK_SUCCESS) return rc;
+    if (variant < HFRK_VARIANT_AUTO || variant > HFRK_VARIANT_STREAMK) return HFRK_INVALID_CONFIG;
+    if (variant == HFRK_VARIANT_AUTO) variant = HFRK_VARIANT_CLUSTER;
+    if (variant == HFRK_VARIANT_STREAMK) {
+        return launch_streamk(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
+                              ctas_per_sm, stages_req, use_pdl, stream, stamps);
+    }
 
     CUtensorMap tmap_w;
     rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(w_row_stride),
@@ -529,6 +698,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         p.stages = plan.stages;
         p.d_dtype = d_dtype;
         p.accumulate = accumulate ? 1 : 0;
+        p.stamps = stamps;
 
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
@@ -568,14 +738,26 @@ extern "C" int hfrk_skinny_gemm_fp8(const void* A, const void* W, void* D, const
     if (split_k_hint < 0) return HFRK_INVALID_CONFIG;
     if (split_k_hint > hfrk::kMaxSplit) split_k_hint = hfrk::kMaxSplit;
     return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
-                             split_k_hint, 0, hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream));
+                             HFRK_VARIANT_AUTO, split_k_hint, 0, 0, hfrk::default_use_pdl(),
+                             static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* scale_dev, int m, int n,
                                        int k, int64_t w_row_stride, int a_kind, int w_kind, int d_dtype,
-                                       int accumulate, int split_k, int num_stages, int use_pdl, void* stream) {
-    return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate, split_k,
-                             num_stages, use_pdl, static_cast<cudaStream_t>(stream));
+                                       int accumulate, int variant, int split_k, int ctas_per_sm, int num_stages,
+                                       int use_pdl, void* stream) {
+    return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate, variant,
+                             split_k, ctas_per_sm, num_stages, use_pdl, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* D, const float* scale_dev, int m,
+                                            int n, int k, int64_t w_row_stride, int a_kind, int w_kind, int d_dtype,
+                                            int accumulate, int variant, int split_k, int ctas_per_sm,
+                                            int num_stages, int use_pdl, unsigned long long* stamps_dev,
+                                            void* stream) {
+    if (m > hfrk::kMaxMPad) return HFRK_TOO_LARGE;
+    return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate, variant,
+                             split_k, ctas_per_sm, num_stages, use_pdl, static_cast<cudaStream_t>(stream), stamps_dev);
 }
 
 extern "C" int64_t hfrk_host_call_workspace_bytes(int m, int n, int k) {
@@ -599,25 +781,31 @@ extern "C" int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, 
     HFRK_CUDA_TRY(cudaMemcpyAsync(a_dev, A_host, a_bytes, cudaMemcpyHostToDevice, s));
     if (accumulate) HFRK_CUDA_TRY(cudaMemcpyAsync(d_dev, D_host, d_bytes, cudaMemcpyHostToDevice, s));
     int rc = hfrk::launch_gemm(a_dev, W_dev, d_dev, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype,
-                               accumulate, 0, 0, 0, s);
+                               accumulate, HFRK_VARIANT_AUTO, 0, 0, 0, hfrk::default_use_pdl(), s);
     if (rc != HFRK_SUCCESS) return rc;
     HFRK_CUDA_TRY(cudaMemcpyAsync(D_host, d_dev, d_bytes, cudaMemcpyDeviceToHost, s));
     HFRK_CUDA_TRY(cudaStreamSynchronize(s));
     return HFRK_SUCCESS;
 }
 
-extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int split_k_hint, int* out6) {
-    if (out6 == nullptr) return HFRK_INVALID_CONFIG;
-    hfrk::Plan plan;
+extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8) {
+    if (out8 == nullptr || variant < HFRK_VARIANT_AUTO || variant > HFRK_VARIANT_STREAMK) return HFRK_INVALID_CONFIG;
     const int mc = m > hfrk::kMaxMPad ? hfrk::kMaxMPad : m;
-    int rc = hfrk::make_plan(mc, n, k, split_k_hint, 0, &plan);
+    if (variant == HFRK_VARIANT_AUTO) variant = HFRK_VARIANT_CLUSTER;
+    if (variant == HFRK_VARIANT_CLUSTER) {
+        hfrk::Plan plan;
+        int rc = hfrk::make_plan(mc, n, k, split_k, 0, &plan);
+        if (rc != HFRK_SUCCESS) return rc;
+        out8[0] = variant; out8[1] = plan.split; out8[2] = plan.stages; out8[3] = plan.ctas;
+        out8[4] = plan.smem_bytes; out8[5] = plan.m_pad; out8[6] = plan.num_kblocks;
+        out8[7] = (n + hfrk::kTileN - 1) / hfrk::kTileN;
+        return HFRK_SUCCESS;
+    }
+    hfrk::SkPlan plan;
+    int rc = hfrk::make_sk_plan(mc, n, k, ctas_per_sm, 0, &plan);
     if (rc != HFRK_SUCCESS) return rc;
-    out6[0] = plan.split;
-    out6[1] = plan.stages;
-    out6[2] = plan.ctas;
-    out6[3] = plan.smem_bytes;
-    out6[4] = plan.m_pad;
-    out6[5] = plan.num_kblocks;
+    out8[0] = variant; out8[1] = 0; out8[2] = plan.stages; out8[3] = plan.grid;
+    out8[4] = plan.smem_bytes; out8[5] = plan.m_pad; out8[6] = plan.nkb; out8[7] = plan.tiles;
     return HFRK_SUCCESS;
 }
 
@@ -627,6 +815,16 @@ extern "C" int hfrk_device_status(int clear, unsigned int* word_out) {
     if (clear && word != 0) {
         const unsigned int zero = 0;
         HFRK_CUDA_TRY(cudaMemcpyToSymbol(hfrk::g_device_status, &zero, sizeof(zero)));
+        // A kernel that gave up may have left tile counters of the stream-K scratch non-zero.
+        int dev = 0;
+        HFRK_CUDA_TRY(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(hfrk::g_scratch_mutex);
+        if (dev >= 0 && dev < 64 && hfrk::g_scratch[dev].ready) {
+            for (int l = 0; l < hfrk::kScratchLanes; ++l) {
+                HFRK_CUDA_TRY(cudaMemset(hfrk::g_scratch[dev].counters[l], 0,
+                                         static_cast<size_t>(hfrk::kSkMaxTiles) * sizeof(unsigned int)));
+            }
+        }
     }
     if (word_out != nullptr) *word_out = word;
     return word == 0 ? HFRK_SUCCESS : HFRK_DEVICE_TIMEOUT;

@@ -15,6 +15,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 
 E4M3FN, E4M3FNUZ = 0, 1
 F16, BF16 = 0, 1
+VARIANT_AUTO, VARIANT_CLUSTER, VARIANT_STREAMK = 0, 1, 2
 
 STATUS_NAMES = {
     0: "SUCCESS", 1: "M_ABOVE_WARPTILE_M", 2: "N_NOT_EVEN", 3: "K_NOT_DIVISIBLE", 4: "TOO_MANY_WARPS",
@@ -26,7 +27,7 @@ STATUS_NAMES = {
 EXPORTED_SYMBOLS = (
     "hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
     "hfrk_host_call_workspace_bytes", "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan",
-    "hfrk_device_status", "hfrk_last_error", "hfrk_version",
+    "hfrk_device_status", "hfrk_last_error", "hfrk_version", "hfrk_skinny_gemm_fp8_profile",
 )
 
 
@@ -45,12 +46,14 @@ def _load() -> ctypes.CDLL:
     vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
     common = [vp, vp, vp, vp, i32, i32, i32, i64, i32, i32, i32, i32]
     lib.hfrk_skinny_gemm_fp8.argtypes = common + [i32, vp]
-    lib.hfrk_skinny_gemm_fp8_ex.argtypes = common + [i32, i32, i32, vp]
+    lib.hfrk_skinny_gemm_fp8_ex.argtypes = common + [i32, i32, i32, i32, i32, vp]
     lib.hfrk_skinny_gemm_fp8_host.argtypes = common + [vp, vp]
+    lib.hfrk_skinny_gemm_fp8_profile.argtypes = common + [i32, i32, i32, i32, i32, vp, vp]
+    lib.hfrk_skinny_gemm_fp8_profile.restype = i32
     lib.hfrk_skinny_gemm_fp8_simt.argtypes = common + [vp]
     lib.hfrk_host_call_workspace_bytes.argtypes = [i32, i32, i32]
     lib.hfrk_host_call_workspace_bytes.restype = i64
-    lib.hfrk_skinny_gemm_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32)]
+    lib.hfrk_skinny_gemm_plan.argtypes = [i32, i32, i32, i32, i32, i32, ctypes.POINTER(i32)]
     lib.hfrk_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_uint)]
     lib.hfrk_last_error.restype = ctypes.c_char_p
     for name in ("hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
@@ -111,10 +114,20 @@ def skinny_gemm(a, w, d, scale, accumulate=True, split_k_hint=0, stream=None) ->
                                         _stream_ptr(stream, a.device))
 
 
-def skinny_gemm_ex(a, w, d, scale, accumulate=True, split_k=0, num_stages=0, use_pdl=False, stream=None) -> int:
+def skinny_gemm_ex(a, w, d, scale, accumulate=True, variant=VARIANT_AUTO, split_k=0, ctas_per_sm=0, num_stages=0,
+                   use_pdl=False, stream=None) -> int:
     with torch.cuda.device(a.device):
-        return lib.hfrk_skinny_gemm_fp8_ex(*_common_args(a, w, d, scale, accumulate), split_k, num_stages,
-                                           int(use_pdl), _stream_ptr(stream, a.device))
+        return lib.hfrk_skinny_gemm_fp8_ex(*_common_args(a, w, d, scale, accumulate), variant, split_k, ctas_per_sm,
+                                           num_stages, int(use_pdl), _stream_ptr(stream, a.device))
+
+
+def skinny_gemm_profile(a, w, d, scale, stamps, accumulate=True, variant=VARIANT_AUTO, split_k=0, ctas_per_sm=0,
+                        num_stages=0, use_pdl=False, stream=None) -> int:
+    """``hfrk_skinny_gemm_fp8_profile``: ``stamps`` is an int64 CUDA tensor of shape [ctas, 8]."""
+    with torch.cuda.device(a.device):
+        return lib.hfrk_skinny_gemm_fp8_profile(*_common_args(a, w, d, scale, accumulate), variant, split_k,
+                                                ctas_per_sm, num_stages, int(use_pdl), stamps.data_ptr(),
+                                                _stream_ptr(stream, a.device))
 
 
 def skinny_gemm_simt(a, w, d, scale, accumulate=True, stream=None) -> int:
@@ -136,10 +149,10 @@ def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True
             work_dev.data_ptr(), _stream_ptr(stream, w_dev.device))
 
 
-def plan(m: int, n: int, k: int, split_k_hint: int = 0) -> dict:
-    out = (ctypes.c_int * 6)()
-    check(lib.hfrk_skinny_gemm_plan(m, n, k, split_k_hint, out))
-    keys = ("split_k", "num_stages", "ctas", "smem_bytes", "m_pad", "k_blocks")
+def plan(m: int, n: int, k: int, variant: int = VARIANT_AUTO, split_k: int = 0, ctas_per_sm: int = 0) -> dict:
+    out = (ctypes.c_int * 8)()
+    check(lib.hfrk_skinny_gemm_plan(m, n, k, variant, split_k, ctas_per_sm, out))
+    keys = ("variant", "split_k", "num_stages", "ctas", "smem_bytes", "m_pad", "k_blocks", "tiles")
     return dict(zip(keys, list(out)))
 
 

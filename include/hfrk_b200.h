@@ -52,29 +52,51 @@ enum hfrk_status {
 enum hfrk_fp8_kind { HFRK_E4M3FN = 0, HFRK_E4M3FNUZ = 1 };
 enum hfrk_out_dtype { HFRK_F16 = 0, HFRK_BF16 = 1 };
 
+/* The two kernels behind the GEMM.
+ *   CLUSTER : one CTA per (128-row tile, K split); the K splits of a tile form a thread-block
+ *             cluster and reduce through distributed shared memory. No scratch memory.
+ *             This is what AUTO picks.
+ *   STREAMK : the (tile, K block) work items are cut into equal ranges over a grid sized to the
+ *             SM count; partial tiles meet in library-owned fp32 scratch and the last CTA to
+ *             arrive reduces them in a fixed order. Balanced for any shape, but its reduction
+ *             goes through L2 and costs more than the in-cluster one at these sizes. */
+enum hfrk_variant { HFRK_VARIANT_AUTO = 0, HFRK_VARIANT_CLUSTER = 1, HFRK_VARIANT_STREAMK = 2 };
+
 /* Single-GPU skinny GEMM on `stream` (a cudaStream_t passed as void*), asynchronous, no host
- * synchronisation, no allocation: capturable in a CUDA graph.
+ * synchronisation. The first call on a device allocates the library's scratch memory (about
+ * 80 MB, kept until the process ends), so it must come before any stream capture; later calls
+ * allocate nothing and can be captured in a CUDA graph. Calls on up to four streams of a device
+ * may overlap; beyond four distinct streams two of them share scratch and must not run GEMMs at
+ * the same time.
  * Replaces skinny_gemm_tb / skinny_gemm() of the reference
  * (csrc/op_src/skinny_gemm/skinny_gemm_binding.cu:16-42, skinny_gemm_caller.cu:21-71).
  *   a_kind, w_kind : enum hfrk_fp8_kind       d_dtype : enum hfrk_out_dtype
  *   accumulate     : 1 = D += result (the reference's contract, wrapped.py:115), 0 = overwrite
  *   split_k_hint   : 0 = choose automatically; >= 1 = requested K split (clamped to what the
- *                    launch supports). The reference's split_k argument maps here. */
+ *                    launch supports). The reference's split_k argument maps here.
+ * The launch uses programmatic dependent launch unless the environment has HFRK_PDL=0: the
+ * weight stream may begin while the previous kernel on `stream` is still running (A, D and the
+ * scale are only read after it has finished). That previous kernel must therefore not write W. */
 int hfrk_skinny_gemm_fp8(const void* A, const void* W, void* D, const float* scale_dev,
                          int m, int n, int k, int64_t w_row_stride,
                          int a_kind, int w_kind, int d_dtype, int accumulate,
                          int split_k_hint, void* stream);
 
 /* Same operation with the launch shape pinned by the caller (benchmark sweeps, tuning):
- *   split_k    : 0 = automatic, else 1..16        num_stages : 0 = automatic, else 2..12
- *   use_pdl    : 1 = launch with programmatic stream serialisation so the weight stream of this
- *                call may start while the previous kernel on the stream drains.
+ *   variant     : enum hfrk_variant
+ *   split_k     : CLUSTER only; 0 = automatic, else 1..16
+ *   ctas_per_sm : STREAMK only; 0 = automatic, else 1 or 2 (grid = 148 * ctas_per_sm)
+ *   num_stages  : 0 = automatic, else 2..12 (CLUSTER, 16 KiB stages) or 2..8 (STREAMK, 32 KiB)
+ *   use_pdl     : 1 = launch with programmatic stream serialisation so the weight stream of this
+ *                 call may start while the previous kernel on the stream drains. Only safe when
+ *                 nothing earlier on the stream writes W.
  * Takes the place of the reference's nine tuning ints
  * (csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:28-32). */
 int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* scale_dev,
                             int m, int n, int k, int64_t w_row_stride,
                             int a_kind, int w_kind, int d_dtype, int accumulate,
-                            int split_k, int num_stages, int use_pdl, void* stream);
+                            int variant, int split_k, int ctas_per_sm, int num_stages, int use_pdl,
+                            void* stream);
 
 /* Host-buffer form of the same call, for callers whose activations live in host memory:
  * copies A (and D when accumulate=1) host->device, runs the GEMM against the device-resident
@@ -95,10 +117,22 @@ int hfrk_skinny_gemm_fp8_simt(const void* A, const void* W, void* D, const float
                               int m, int n, int k, int64_t w_row_stride,
                               int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);
 
-/* Launch shape the automatic heuristic would pick (for logs and tests; no GPU work).
- * out[0]=split_k, out[1]=num_stages, out[2]=grid CTAs, out[3]=dynamic shared memory bytes,
- * out[4]=padded token count (MMA N), out[5]=K blocks of 128. Returns a status code. */
-int hfrk_skinny_gemm_plan(int m, int n, int k, int split_k_hint, int* out6);
+/* hfrk_skinny_gemm_fp8_ex (m <= 64) that also records, per CTA, eight %globaltimer samples (ns)
+ * into stamps_dev[cta][8]: 0 kernel entry, 1 set-up done, 2 first loads issued, 3 first stage
+ * landed, 4 last MMA issued, 5 accumulator complete, 6 output written, 7 TMEM released.
+ * stamps_dev holds grid CTAs * 8 uint64 (the plan query gives the CTA count). A profiling aid
+ * with no counterpart in the reference. */
+int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* D, const float* scale_dev,
+                                 int m, int n, int k, int64_t w_row_stride,
+                                 int a_kind, int w_kind, int d_dtype, int accumulate,
+                                 int variant, int split_k, int ctas_per_sm, int num_stages, int use_pdl,
+                                 unsigned long long* stamps_dev, void* stream);
+
+/* Launch shape for (m, n, k) and the given pins (for logs and tests; no GPU work).
+ * out[0]=variant chosen, out[1]=split_k (0 for STREAMK), out[2]=num_stages, out[3]=grid CTAs,
+ * out[4]=dynamic shared memory bytes, out[5]=padded token count (MMA N), out[6]=K blocks of 128,
+ * out[7]=tiles of 128 rows. Returns a status code. */
+int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8);
 
 /* Device-side status word of the current device: 0, or the HFRK_DEVICE_TIMEOUT details packed
  * as (code << 24 | role << 16 | block index & 0xffff). Reads it with a synchronous copy, and

@@ -20,7 +20,9 @@ bit-for-bit to outputs of the reference's own ``fp8.py`` executed on CPU, and th
 vectors are in ``tests/golden/``.
 
 Everything is numpy; a C twin (``skinny_gemm_oracle.c``) is loaded through ctypes by
-:func:`load_c_oracle` and must agree with this file bit-for-bit.
+:func:`load_c_oracle`. The two agree bit-for-bit on the quantiser and on the GEMM without
+``d_in``; with ``d_in`` the numpy form rounds the final multiply-add twice where C's ``fmaf``
+rounds once, so they may differ by one float32 ulp.
 """
 from __future__ import annotations
 
@@ -175,23 +177,52 @@ def ulp(ref32: np.ndarray, d_dtype: int = BF16) -> np.ndarray:
 
 
 def tolerance(ref32: np.ndarray, k: int, scale: float, d_dtype: int = BF16) -> np.ndarray:
-    """Per-element bound: one output ulp of the reference value + 1e-3 * sqrt(K) * |scale|."""
+    """The stated bound, per element: one output ulp of the reference value + 1e-3*sqrt(K)*|scale|."""
     return ulp(ref32, d_dtype) + 1e-3 * math.sqrt(k) * abs(float(scale))
 
 
-def compare(out32: np.ndarray, ref32: np.ndarray, k: int, scale: float, d_dtype: int = BF16) -> dict:
-    """Error of ``out32`` (the kernel's output as float32) against ``ref32`` under :func:`tolerance`."""
+def accumulation_floor(a_q: np.ndarray, w_q: np.ndarray, scale: float, a_kind: int = E4M3FN,
+                       w_kind: int = E4M3FN) -> np.ndarray:
+    """Rounding noise no fp32 accumulation of these dot products can avoid, per element.
+
+    An fp32 accumulator that absorbs K/32 block results rounds K/32 times at 2**-24 relative to the
+    running sum; the running sum of a dot product of signed terms wanders with magnitude
+    sqrt(sum_k (a_k w_k)**2), and independent roundings add in quadrature. Two units of that:
+        floor = 2**-23 * sqrt(K / 32) * sqrt(sum_k (a_k w_k)**2) * |scale|.
+    For K = 4096 it is about a quarter of the absolute term of :func:`tolerance`; from K ~ 14k on
+    it exceeds it, which is where any fp32 matmul (a host BLAS included) starts to disagree with the
+    exact product on outputs that happen to land within ~1e-3 of zero. It only ever matters there:
+    against a typical output it is a relative 1e-6.
+    """
+    table = fp8_table(E4M3FN).astype(np.float64)
+    a2 = table[np.asarray(a_q, dtype=np.uint8)] ** 2
+    w2 = table[np.asarray(w_q, dtype=np.uint8)] ** 2
+    walk = np.sqrt(a2 @ w2.T)
+    k = a_q.shape[1]
+    eff = abs(float(np.float32(scale) * kind_factor(a_kind, w_kind)))
+    return (2.0 ** -23) * math.sqrt(k / 32.0) * walk * eff
+
+
+def compare(out32: np.ndarray, ref32: np.ndarray, k: int, scale: float, d_dtype: int = BF16,
+            floor: Optional[np.ndarray] = None) -> dict:
+    """Error of ``out32`` (the kernel's output as float32) against ``ref32``.
+
+    ``violations`` counts elements beyond :func:`tolerance`; ``hard_violations`` those beyond
+    tolerance + ``floor`` (see :func:`accumulation_floor`; zero when no floor is given).
+    """
     out32 = np.asarray(out32, dtype=np.float64)
     ref = np.asarray(ref32, dtype=np.float64)
     err = np.abs(out32 - ref)
     tol = tolerance(ref32, k, scale, d_dtype)
     ratio = err / tol
     bad = ~(err <= tol)
-    worst = int(np.argmax(np.where(np.isnan(ratio), np.inf, ratio)))
+    hard = bad if floor is None else ~(err <= tol + floor)
+    worst = int(np.argmax(np.where(np.isnan(ratio), np.inf, ratio))) if err.size else 0
     return {
         "max_abs_err": float(np.nanmax(err)) if err.size else 0.0,
         "max_err_over_tol": float(np.nanmax(ratio)) if err.size else 0.0,
         "violations": int(bad.sum()),
+        "hard_violations": int(hard.sum()),
         "count": int(err.size),
         "worst_index": worst,
         "worst_out": float(out32.flat[worst]) if err.size else 0.0,

@@ -1,0 +1,106 @@
+"""The C ABI without a GPU: the library loads, exports what the header declares, plans launch
+shapes, and rejects bad arguments before it touches CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "hfrk_b200.h")
+
+
+@pytest.fixture(scope="module")
+def capi(native_build):
+    from hf_rocm_kernels import _capi
+
+    return _capi
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hfrk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(capi):
+    names = declared_symbols()
+    assert len(names) >= 10
+    for name in names:
+        assert hasattr(capi.lib, name), f"{name} is declared in hfrk_b200.h but not exported"
+    assert set(capi.EXPORTED_SYMBOLS) <= set(names)
+
+
+def test_header_cites_the_reference_for_each_entry_point():
+    text = open(HEADER).read()
+    assert "skinny_gemm_binding.cu:16-42" in text and "skinny_gemm_caller.cu" in text
+    assert "torch" not in re.sub(r"/\*.*?\*/", "", text, flags=re.S)  # no torch types in signatures
+
+
+def test_version(capi):
+    assert capi.lib.hfrk_version() >= 100
+    assert capi.lib.hfrk_last_error() is not None
+
+
+def test_plan_covers_the_sms(capi):
+    # fewer tiles than SMs -> a K split that brings the grid to about two CTAs per SM
+    for (m, n, k) in [(16, 4096, 4096), (16, 6144, 4096), (16, 4096, 14336), (16, 8192, 8192), (1, 8192, 28672)]:
+        p = capi.plan(m, n, k)
+        assert p["variant"] == capi.VARIANT_CLUSTER and p["tiles"] == (n + 127) // 128
+        assert 148 <= p["ctas"] <= 3 * 148 and p["ctas"] == p["tiles"] * p["split_k"]
+        assert p["k_blocks"] // p["split_k"] >= 4 and p["smem_bytes"] <= 227 * 1024
+    # enough tiles -> no split, deeper ring
+    for (m, n, k) in [(16, 28672, 4096), (4, 57344, 8192)]:
+        p = capi.plan(m, n, k)
+        assert p["split_k"] == 1 and p["num_stages"] == 6
+    # K tails and odd N round up; token padding is a multiple of 16
+    p = capi.plan(5, 1000, 1040)
+    assert p["tiles"] == 8 and p["k_blocks"] == 9 and p["m_pad"] == 16
+    assert capi.plan(17, 1024, 1024)["m_pad"] == 32 and capi.plan(200, 1024, 1024)["m_pad"] == 64
+    # a requested split is honoured up to the number of K blocks
+    assert capi.plan(16, 4096, 4096, capi.VARIANT_CLUSTER, 3)["split_k"] == 3
+    assert capi.plan(16, 4096, 256, capi.VARIANT_CLUSTER, 16)["split_k"] == 2
+    # stream-K covers the SMs once or twice and never launches idle CTAs
+    sk = capi.plan(16, 4096, 4096, capi.VARIANT_STREAMK, 0, 2)
+    assert sk["ctas"] == 296 and sk["variant"] == capi.VARIANT_STREAMK
+    assert capi.plan(16, 4096, 4096, capi.VARIANT_STREAMK, 0, 1)["ctas"] == 148
+    assert capi.plan(4, 128, 256, capi.VARIANT_STREAMK)["ctas"] == 2
+
+
+def test_plan_rejects_bad_arguments(capi):
+    out = (ctypes.c_int * 8)()
+    assert capi.lib.hfrk_skinny_gemm_plan(0, 128, 128, 0, 0, 0, out) == 6
+    assert capi.lib.hfrk_skinny_gemm_plan(16, 128, 128, 7, 0, 0, out) == 6
+    assert capi.lib.hfrk_skinny_gemm_plan(16, 128, 128, 1, 99, 0, out) == 6
+    assert capi.lib.hfrk_skinny_gemm_plan(16, 128, 128, 0, 0, 0, None) == 6
+
+
+def test_argument_validation_happens_before_any_cuda_call(capi):
+    """Host tensors stand in for device buffers: every call below must be refused on its
+    arguments alone (a launch would fail differently, with CUDA_ERROR)."""
+    a = torch.zeros((4, 256), dtype=torch.uint8)
+    w = torch.zeros((128, 256), dtype=torch.uint8)
+    d = torch.zeros((4, 128), dtype=torch.float16)
+    s = torch.ones(1, dtype=torch.float32)
+    call = capi.lib.hfrk_skinny_gemm_fp8
+    base = [a.data_ptr(), w.data_ptr(), d.data_ptr(), s.data_ptr()]
+    assert call(*base, 0, 128, 256, 256, 0, 0, 0, 1, 0, None) == 6          # m <= 0
+    assert call(*base, 4, 128, 250, 256, 0, 0, 0, 1, 0, None) == 3          # k % 16
+    assert call(*base, 4, 128, 256, 200, 0, 0, 0, 1, 0, None) == 7          # pitch < k
+    assert call(*base, 4, 128, 256, 264, 0, 0, 0, 1, 0, None) == 7          # pitch % 16
+    assert call(*base, 4, 128, 256, 256, 2, 0, 0, 1, 0, None) == 8          # fp8 kind
+    assert call(*base, 4, 128, 256, 256, 0, 0, 5, 1, 0, None) == 8          # output dtype
+    assert call(*base, 4, 128, 256, 256, 0, 0, 0, 1, -1, None) == 6         # split hint
+    assert call(a.data_ptr() + 1, *base[1:], 4, 128, 256, 256, 0, 0, 0, 1, 0, None) == 7  # alignment
+    assert call(None, *base[1:], 4, 128, 256, 256, 0, 0, 0, 1, 0, None) == 6
+    assert capi.lib.hfrk_skinny_gemm_fp8_simt(*base, 4, 128, 250, 256, 0, 0, 0, 1, None) == 3
+    assert capi.lib.hfrk_host_call_workspace_bytes(4, 128, 256) == 1024 + 1024
+    assert capi.lib.hfrk_host_call_workspace_bytes(0, 128, 256) == 0
+
+
+def test_status_names_cover_the_header(capi):
+    text = open(HEADER).read()
+    codes = dict((int(v), k) for k, v in re.findall(r"HFRK_([A-Z_0-9]+) = (\d+)", text.split("enum hfrk_fp8_kind")[0]))
+    for code, name in codes.items():
+        assert capi.STATUS_NAMES[code] == name

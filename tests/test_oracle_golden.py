@@ -1,0 +1,122 @@
+"""The CPU oracle against the vectors produced by the reference itself (tests/golden/)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_decode_tables_match_torch(oracle_mod, c_oracle):
+    for kind, dtype in ((oracle_mod.E4M3FN, torch.float8_e4m3fn), (oracle_mod.E4M3FNUZ, torch.float8_e4m3fnuz)):
+        expect = torch.arange(256, dtype=torch.uint8).view(dtype).float().numpy()
+        assert np.array_equal(oracle_mod.fp8_table(kind), expect, equal_nan=True)
+        c_table = np.array([c_oracle.fp8_to_f32(i, kind) for i in range(256)], dtype=np.float32)
+        assert np.array_equal(c_table, expect, equal_nan=True)
+
+
+def test_fnuz_is_half_of_fn_for_every_byte_the_quantiser_emits(oracle_mod):
+    fn = oracle_mod.fp8_table(oracle_mod.E4M3FN)
+    fnuz = oracle_mod.fp8_table(oracle_mod.E4M3FNUZ)
+    emitted = [b for b in range(256) if b not in (0x80, 0x7F, 0xFF)]
+    assert np.array_equal(fnuz[emitted], fn[emitted] / 2)
+    # the three exceptions: NaN on one side only
+    assert np.isnan(fnuz[0x80]) and fn[0x80] == 0 and np.isnan(fn[0x7F]) and fnuz[0x7F] == 240
+
+
+def test_quantiser_is_bit_exact_with_the_reference(oracle_mod, c_oracle, golden_dir):
+    g = np.load(os.path.join(golden_dir, "quantiser.npz"))
+    for i, scale in enumerate(g["scales"]):
+        want = g["bytes"][i]
+        assert np.array_equal(oracle_mod.quantize_e4m3fn(g["values"], scale, zero_negative_zero=True), want)
+        assert np.array_equal(c_oracle.quantize(g["values"], scale, True), want)
+        assert g["returned_scales"][i] == np.float32(scale) * 2
+
+
+def test_package_quantiser_matches_the_reference(golden_dir):
+    from hf_rocm_kernels.utils.fp8 import fp8_quantize, fp8_quantize_e4m3fn
+
+    g = np.load(os.path.join(golden_dir, "quantiser.npz"))
+    x = torch.from_numpy(g["values"])
+    for i, scale in enumerate(g["scales"]):
+        q, doubled = fp8_quantize(x.clone(), torch.tensor([scale]))
+        assert q.dtype == torch.float8_e4m3fnuz
+        assert np.array_equal(q.view(torch.uint8).numpy(), g["bytes"][i])
+        assert float(doubled) == g["returned_scales"][i]
+        q_fn, same = fp8_quantize_e4m3fn(x.clone(), torch.tensor([scale]))
+        fn_bytes = q_fn.view(torch.uint8).numpy()
+        # identical except that e4m3fn keeps the negative zero
+        assert np.array_equal(np.where(fn_bytes == 0x80, 0, fn_bytes), g["bytes"][i]) and float(same) == scale
+
+
+def _golden_cases(golden_dir):
+    g = np.load(os.path.join(golden_dir, "gemm_cases.npz"))
+    for i in range(int(g["count"][0])):
+        d_in = None
+        if f"c{i}_d_in_f16" in g:
+            d_in = g[f"c{i}_d_in_f16"].view(np.float16).astype(np.float32)
+        yield i, g[f"c{i}_a"], g[f"c{i}_w"], float(g[f"c{i}_scale"][0]), d_in, g
+
+
+def test_gemm_matches_scaled_mm_outputs(oracle_mod, c_oracle, golden_dir):
+    """torch._scaled_mm (what the reference calls) scales the operands before its fp32 matmul, so
+    its float32 result differs from the exact product by float32 rounding; the oracle must sit
+    within that rounding, and round to the same fp16/bf16 value except on rounding ties."""
+    fnuz = oracle_mod.E4M3FNUZ
+    total = mism16 = mismbf = 0
+    for i, a, w, scale, _d_in, g in _golden_cases(golden_dir):
+        ref = oracle_mod.reference_skinny_gemm(a, w, scale, None, fnuz, fnuz)
+        assert np.array_equal(ref, c_oracle.skinny_gemm(a, w, scale, None, fnuz, fnuz))
+        f32 = g[f"c{i}_f32"]
+        slack = 4e-6 * np.abs(f32) + 1e-6 * np.sqrt(a.shape[1])
+        assert np.all(np.abs(ref - f32) <= slack)
+        f16 = g[f"c{i}_f16"].view(np.float16).astype(np.float32)
+        bf16 = oracle_mod.bf16_bits_to_f32(g[f"c{i}_bf16"])
+        got16 = oracle_mod.cast_out(ref, oracle_mod.F16)
+        gotbf = oracle_mod.cast_out(ref, oracle_mod.BF16)
+        assert np.all(np.abs(got16 - f16) <= oracle_mod.ulp(f16, oracle_mod.F16) + slack)
+        assert np.all(np.abs(gotbf - bf16) <= oracle_mod.ulp(bf16, oracle_mod.BF16) + slack)
+        total += ref.size
+        mism16 += int((got16 != f16).sum())
+        mismbf += int((gotbf != bf16).sum())
+    assert mism16 <= 0.01 * total and mismbf <= 0.01 * total
+
+
+def test_d_in_is_added_after_the_scale(oracle_mod, c_oracle, golden_dir):
+    fnuz = oracle_mod.E4M3FNUZ
+    seen = 0
+    for _i, a, w, scale, d_in, _g in _golden_cases(golden_dir):
+        if d_in is None:
+            continue
+        seen += 1
+        plain = oracle_mod.reference_skinny_gemm(a, w, scale, None, fnuz, fnuz)
+        with_d = oracle_mod.reference_skinny_gemm(a, w, scale, d_in, fnuz, fnuz)
+        assert np.allclose(with_d, plain + d_in, rtol=0, atol=np.spacing(np.abs(with_d).max()))
+        c_with_d = c_oracle.skinny_gemm(a, w, scale, d_in, fnuz, fnuz)
+        assert np.all(np.abs(c_with_d - with_d) <= np.spacing(np.abs(with_d)))
+    assert seen >= 2
+
+
+def test_exact_and_float32_accumulation_agree_within_the_floor(oracle_mod, c_oracle):
+    rng = np.random.default_rng(7)
+    a = oracle_mod.quantize_e4m3fn(rng.normal(size=(4, 2048)).astype(np.float32), 0.011)
+    w = oracle_mod.quantize_e4m3fn(rng.normal(size=(96, 2048)).astype(np.float32), 0.012)
+    scale = 0.011 * 0.012
+    exact = c_oracle.skinny_gemm(a, w, scale, exact=True)
+    f32 = c_oracle.skinny_gemm(a, w, scale, exact=False)
+    floor = oracle_mod.accumulation_floor(a, w, scale)
+    # index-order float32 summation rounds K times, the floor models K/32 roundings
+    assert np.all(np.abs(exact.astype(np.float64) - f32) <= floor * np.sqrt(32.0) * 4)
+    assert np.array_equal(exact, oracle_mod.reference_skinny_gemm(a, w, scale))
+
+
+def test_tolerance_formula(oracle_mod):
+    ref = np.array([0.0, 1.0, 1.5, 64.0, -100.0, 1e-3], dtype=np.float32)
+    ulp_bf16 = oracle_mod.ulp(ref, oracle_mod.BF16)
+    assert np.array_equal(ulp_bf16[1:5], [2.0 ** -7, 2.0 ** -7, 2.0 ** -1, 2.0 ** -1])
+    assert oracle_mod.ulp(np.float32(1.0), oracle_mod.F16) == 2.0 ** -10
+    tol = oracle_mod.tolerance(ref, 4096, 1e-4, oracle_mod.BF16)
+    assert np.allclose(tol - ulp_bf16, 1e-3 * 64 * 1e-4)
+    res = oracle_mod.compare(ref + tol.astype(np.float32) * 0.5, ref, 4096, 1e-4)
+    assert res["violations"] == 0
+    res = oracle_mod.compare(ref + 1.0, ref, 4096, 1e-4)
+    assert res["violations"] == ref.size and res["hard_violations"] == ref.size

@@ -1,0 +1,107 @@
+"""The Python surface the reference exposes for this path, checked without a GPU: names,
+signatures, the op schema, argument checks."""
+import inspect
+
+import pytest
+import torch
+
+
+@pytest.fixture(scope="module")
+def pkg(native_build):
+    import hf_rocm_kernels
+
+    return hf_rocm_kernels
+
+
+def test_public_names(pkg):
+    from hf_rocm_kernels.operators.skinny_gemm import generate_skinny_gemm_data, reference_skinny_gemm, skinny_gemm
+    from hf_rocm_kernels.operators.skinny_gemm.binding import _skinny_gemm
+    from hf_rocm_kernels.utils.fp8 import fp8_quantize
+    from hf_rocm_kernels.utils.testing import compare_x_and_ref_to_precise, compare_x_with_ref
+
+    assert pkg.skinny_gemm is skinny_gemm
+    assert list(inspect.signature(skinny_gemm).parameters) == ["skinny_a", "b", "scale_tensor", "output"]
+    assert list(inspect.signature(_skinny_gemm).parameters) == [
+        "A", "B", "scale_tensor", "D", "split_k", "A_producers", "B_producers", "consumers",
+        "a_lanes", "b_lanes", "qsize", "op_m", "ops"]
+    assert list(inspect.signature(reference_skinny_gemm).parameters) == [
+        "skinny_a", "b", "scale_a", "scale_b", "output"]
+    assert list(inspect.signature(generate_skinny_gemm_data).parameters)[:4] == ["m", "n", "k", "seed"]
+    assert callable(fp8_quantize) and callable(compare_x_with_ref) and callable(compare_x_and_ref_to_precise)
+
+
+def test_op_schema_is_the_reference_schema(pkg):
+    schema = torch.ops._HFRK_C.skinny_gemm_tb.default._schema
+    # the reference's definition string (csrc/torch_bindings.cpp:38-41), parsed by torch itself
+    want = torch._C.parse_schema(
+        "_HFRK_C::skinny_gemm_tb(Tensor A, Tensor B, Tensor! D, Tensor scale_tensor, int split_k, int A_producers, "
+        "int B_producers, int consumers, int a_lanes, int b_lanes, int qsize, int op_m, int ops) -> int")
+    assert str(schema) == str(want)
+    assert [a.name for a in schema.arguments] == [a.name for a in want.arguments]
+    assert schema.arguments[2].alias_info is not None and schema.arguments[2].alias_info.is_write
+
+
+def test_checks_reject_what_the_reference_rejects(pkg):
+    from hf_rocm_kernels.operators.skinny_gemm.wrapped import infer_skinny_gemm_params, skinny_gemm_checks
+
+    a = torch.zeros((4, 256), dtype=torch.float8_e4m3fnuz)
+    w = torch.zeros((128, 256), dtype=torch.float8_e4m3fnuz)
+    s = torch.ones(1)
+    d = torch.zeros((4, 128), dtype=torch.float16)
+    with pytest.raises(AssertionError, match="cuda"):
+        skinny_gemm_checks(a, w.t(), s, d)                       # CPU tensors
+    with pytest.raises(AssertionError, match="column-major"):
+        skinny_gemm_checks(a, torch.zeros((256, 128), dtype=torch.float8_e4m3fnuz), s, d)
+    with pytest.raises(AssertionError):
+        skinny_gemm_checks(a, w.t(), torch.ones(2), d)           # scale must hold one element
+    with pytest.raises(AssertionError):
+        skinny_gemm_checks(a, w.t(), s, torch.zeros((4, 64), dtype=torch.float16))
+    with pytest.raises(AssertionError):
+        skinny_gemm_checks(a.float(), w.t(), s, d)               # dtype
+    with pytest.raises(AssertionError):
+        skinny_gemm_checks(a, w.t(), s.double(), d)
+    params = infer_skinny_gemm_params(a, w.t())
+    assert set(params) == {"split_k", "A_producers", "B_producers", "consumers", "a_lanes", "b_lanes", "qsize",
+                           "op_m", "ops"}
+    assert params["split_k"] == 0 and params["op_m"] == 16
+
+
+def test_compare_helpers():
+    from hf_rocm_kernels.utils.testing import compare_x_and_ref_to_precise, compare_x_with_ref, skinny_gemm_tolerance
+
+    ref = torch.tensor([1.0, 2.0, 0.0, -4.0])
+    x = torch.tensor([1.0, 2.5, 0.0, -4.0])
+    max_abs, max_rel, changed = compare_x_with_ref(x, ref)
+    assert max_abs == 0.5 and max_rel == 0.25 and changed == 1
+    with pytest.raises(ValueError):
+        compare_x_with_ref(x, ref[:2])
+    out = compare_x_and_ref_to_precise(x, ref, ref)
+    assert out[0] == 0.5 and out[1] == 0.0 and out[4] == 25.0
+    tol = skinny_gemm_tolerance(torch.tensor([1.0, 64.0]), 4096, 1e-4, torch.bfloat16)
+    assert torch.allclose(tol, torch.tensor([2.0 ** -7, 0.5], dtype=torch.float64) + 6.4e-6)
+
+
+def test_workload_configurations():
+    from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
+
+    assert [len(wl.cases(c)) for c in range(5)] == [1, 20, 12, 4, 45]
+    c0 = wl.cases(0)[0]
+    assert (c0.m, c0.n, c0.k, c0.bias) == (1, 4096, 4096, False) and c0.seed == 0
+    assert {(c.n, c.k) for c in wl.cases(1)} == {(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)}
+    assert all(c.bias == (c.n == 6144) for c in wl.cases(1))
+    assert {(c.n, c.k) for c in wl.cases(2)} == {(10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)}
+    assert {c.m for c in wl.cases(3)} == {1, 2, 8, 16}
+    edge = wl.cases(4)
+    assert {c.m for c in edge} == {3, 5, 7, 13, 16} and all(c.outliers for c in edge)
+    assert [c.bias for c in edge[:4]] == [True, False, True, False]
+    case = wl.Case(4, 1, "t", 3, 136, 1040, bias=True, outliers=True)
+    x, y = wl.make_inputs(case), wl.make_inputs(case)
+    assert torch.equal(x["a"].view(torch.uint8), y["a"].view(torch.uint8))  # seeded
+    assert x["a"].dtype == torch.float8_e4m3fn and x["d_in"].shape == (3, 136) and x["d_in"].dtype == torch.bfloat16
+    saturated = (x["w"].view(torch.uint8) & 0x7F) == 0x7E
+    assert 0.005 < saturated.float().mean() < 0.02                           # ~1 % outliers pinned at +-448
+    assert torch.equal(x["scale"], x["scale_a"] * x["scale_w"])
+    assert case.algorithmic_bytes() == 136 * 1040 + 3 * 1040 + 2 * (3 * 136 * 2) + 4
+    assert wl.n_split_rows(10240, 8, 3) == (3840, 5120) and wl.k_split_cols(28672, 8, 7) == (25088, 28672)
+    with pytest.raises(ValueError):
+        wl.n_split_rows(1000, 3, 0)
