@@ -1,0 +1,376 @@
+"""Benchmark of the FP8 skinny GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-detail]
+
+One *step* is one pass over the Llama-3-8B decode projections (configuration 1 of the benchmark
+specification: M in {1,2,4,8,16} x {qkv 6144x4096 (+bias), o_proj 4096x4096, gate_up 28672x4096,
+down 4096x14336}, 20 calls), every call on its own weight matrix, so a step streams 1.09 GB of
+distinct weights -- about nine times the L2 -- and nothing is re-read from cache between calls or
+between steps. The 20 calls are captured once in a CUDA graph through the public torch op (the
+reference times its op the same way: operators/skinny_gemm/benchmarking_fn.py:62-92) and the graph
+is replayed once per step.
+
+Printed: ONE JSON line. ``value`` is the achieved HBM bandwidth over the timed steps (algorithmic
+bytes of every call / device time, inputs resident in HBM), whole job over all ranks. ``e2e`` is
+the same metric through the C ABI's host-buffer call: activations (and the bias) come from pinned
+host memory and the result is read back to the host inside the timed region, every call; weights
+stay resident (they are model state). With N > 1 (launched by torchrun, one rank per GPU) every
+rank runs the same per-GPU workload on its own shard of a column-parallel layer, no collective on
+the data path: weak scaling.
+
+``--impl reference`` times the CPU port of the reference's semantics (oracle/cpu_baseline.py) on
+the host cores instead; rank 0 only.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "hf-rocm-kernels_b200"))
+
+METRIC = "fp8_skinny_gemm_hbm_bandwidth"
+UNIT = "TB/s"
+WORKLOAD = "llama3_8b_decode_projections_fp8_e4m3_bf16out_M1-16 (configuration 1)"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_hbm_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, copy kernel)"
+    except Exception:
+        return 6650.0, "fallback (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """Samples the SM clock and the throttle reasons of one GPU through NVML (read-only queries)
+    every few milliseconds while the timed region runs."""
+
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+
+    def __init__(self, index: int):
+        self.index = index
+        self.sm = []
+        self.mask = 0
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.thread = None
+        self.error = None
+
+    def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            # CUDA_VISIBLE_DEVICES may renumber devices: resolve the NVML handle through the PCI bus id
+            import torch
+
+            bus = torch.cuda.get_device_properties(self.index).pci_bus_id if hasattr(
+                torch.cuda.get_device_properties(self.index), "pci_bus_id") else None
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            if bus is not None:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    if int(pynvml.nvmlDeviceGetPciInfo(h).bus) == int(bus):
+                        self.handle = h
+                        break
+            self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # NVML missing: report it rather than fail the benchmark
+            self.error = repr(exc)[:120]
+            return
+        self.thread = threading.Thread(target=self._poll, daemon=True)
+        self.thread.start()
+
+    def _poll(self):
+        while not self.stop_flag.is_set():
+            try:
+                self.sm.append(float(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)))
+                self.mask |= int(self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+            except Exception as exc:
+                self.error = repr(exc)[:120]
+                return
+            time.sleep(0.002)
+
+    def stop(self):
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=1)
+        reasons = sorted(name for name, bit in self.REASONS.items() if self.mask & bit)
+        out = {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+               "reasons": reasons, "samples": len(self.sm)}
+        if self.error:
+            out["error"] = self.error
+        return out
+
+
+def build_workload(dev, wl, torch):
+    """Per case: inputs on the device (drawn by a device generator: values N(0,1), per-tensor
+    e4m3fn quantisation) plus pinned host copies of the per-step inputs for the e2e leg."""
+    items = []
+    for case in wl.cases(1):
+        inp = wl.make_inputs(case, device=str(dev))
+        d0 = inp["d_in"] if inp["d_in"] is not None else torch.zeros((case.m, case.n), dtype=torch.bfloat16, device=dev)
+        items.append({
+            "case": case, "a": inp["a"], "w": inp["w"], "scale": inp["scale"], "d0": d0, "d": d0.clone(),
+            "a_host": inp["a"].cpu().pin_memory(), "d_host": d0.cpu().pin_memory(),
+            "d0_host": d0.cpu().pin_memory(),
+        })
+    return items
+
+
+def self_check(items, capi, torch):
+    """One call per shape against the SIMT diagnostic kernel: a timed kernel that does not do the
+    work would show up here, before any number is printed."""
+    for it in items:
+        if it["case"].m != 16:
+            continue
+        got = it["d0"].clone()
+        want = it["d0"].clone()
+        capi.check(capi.skinny_gemm(it["a"], it["w"], got, it["scale"]))
+        capi.check(capi.skinny_gemm_simt(it["a"], it["w"], want, it["scale"]))
+        torch.cuda.synchronize()
+        diff = (got.float() - want.float()).abs().max().item()
+        ref_mag = want.float().abs().max().item()
+        if not diff <= 0.02 * ref_mag + 1e-3:
+            raise RuntimeError(f"self-check failed for {it['case'].name}: max diff {diff} vs magnitude {ref_mag}")
+
+
+def time_case_rotating(it, skinny_gemm, torch, warmups=8, iters=24):
+    """us per call of one case the way the reference measures it: one graph of G back-to-back calls
+    on G different weight matrices (G matrices total at least twice the L2), replayed."""
+    case = it["case"]
+    g_count = max(8, -(-2 * L2_BYTES // case.weight_bytes))
+    pool = [it["w"]] + [it["w"].clone() for _ in range(g_count - 1)]
+    for k, extra in enumerate(pool[1:]):  # make the copies different matrices
+        extra.view(torch.uint8).copy_(torch.roll(it["w"].view(torch.uint8), shifts=k + 1, dims=0))
+    out = it["d0"].clone()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        skinny_gemm(it["a"], pool[0].t(), it["scale"], out)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for w in pool:
+                skinny_gemm(it["a"], w.t(), it["scale"], out)
+        times = []
+        for i in range(warmups + iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            e1.synchronize()
+            if i >= warmups:
+                times.append(e0.elapsed_time(e1) * 1000.0 / g_count)
+    del pool
+    return statistics.median(times)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import hf_rocm_kernels
+    from hf_rocm_kernels import _capi as capi
+    from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    items = build_workload(dev, wl, torch)
+    self_check(items, capi, torch)
+    step_bytes = sum(it["case"].algorithmic_bytes() for it in items)
+    step_weight_bytes = sum(it["case"].weight_bytes for it in items)
+
+    # ---- the device-resident leg: one CUDA graph of the 20 calls, through the torch op
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for it in items:
+            hf_rocm_kernels.skinny_gemm(it["a"], it["w"].t(), it["scale"], it["d"])
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for it in items:
+                hf_rocm_kernels.skinny_gemm(it["a"], it["w"].t(), it["scale"], it["d"])
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        e1.synchronize()
+        barrier()
+        device_ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+
+    # ---- the end-to-end leg: host buffers through the C ABI, copies inside the timed region
+    work = torch.empty(max(capi.lib.hfrk_host_call_workspace_bytes(c.m, c.n, c.k) for c in wl.cases(1)),
+                       dtype=torch.uint8, device=dev)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        for it in items:
+            it["d_host"].copy_(it["d0_host"])                      # the caller's bias-filled output buffer
+            capi.check(capi.skinny_gemm_host(it["a_host"], it["w"], it["d_host"], it["scale"], work,
+                                             accumulate=it["case"].bias))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1000.0
+    barrier()
+    h2d = sum(c.m * c.k + (2 * c.m * c.n if c.bias else 0) for c in wl.cases(1))
+    d2h = sum(2 * c.m * c.n for c in wl.cases(1))
+
+    # ---- per-case times (rank 0 of a single-GPU run only; bounded)
+    detail = None
+    if world == 1 and not args.no_detail:
+        detail = []
+        for it in items:
+            us = time_case_rotating(it, hf_rocm_kernels.skinny_gemm, torch)
+            c = it["case"]
+            detail.append({"case": c.name, "us_per_call": round(us, 2),
+                           "hbm_tbps": round(c.algorithmic_bytes() / us / 1e6, 3),
+                           "weight_tbps": round(c.weight_bytes / us / 1e6, 3)})
+
+    status_code, status_word = capi.device_status(clear=True)
+    if status_code != 0:
+        raise RuntimeError(f"device status word {status_word:#x}: a bounded wait ran out during the benchmark")
+
+    # ---- max over ranks
+    times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    device_ms, e2e_ms = times.tolist()
+
+    if rank == 0:
+        peak_gbs, peak_source = measured_hbm_peak_gbs()
+        ms_per_step = device_ms / args.steps
+        value = world * step_bytes / (ms_per_step * 1e-3) / 1e12
+        per_gpu_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
+        e2e_value = world * step_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 out)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "calls_per_step": len(items),
+                       "weight_bytes_per_step": step_weight_bytes, "algorithmic_bytes_per_step": step_bytes,
+                       "l2": "each call has its own weight matrix; a step streams 1.09 GB (>> 126 MB L2)",
+                       "timing": "CUDA events on the launching stream around K graph replays, max over ranks",
+                       "us_per_call_mean": round(ms_per_step * 1e3 / len(items), 3),
+                       "weight_stream_tbps": round(world * step_weight_bytes / (ms_per_step * 1e-3) / 1e12, 4)},
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu_gbs, 1), "peak": peak_gbs, "unit": "GB/s",
+                         "frac": round(per_gpu_gbs / peak_gbs, 4), "traffic": None, "peak_source": peak_source,
+                         "kernel": "skinny_gemm_fp8_sm100_kernel", "launches": args.steps * len(items)},
+            "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "note": "host activations/bias in, host result out, every call; weights resident"},
+            "gpu_launches": args.steps * len(items),
+            "clocks": clocks,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(torch, wl)
+        if detail is not None:
+            line["detail"] = detail
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_sample(torch, wl):
+    """The bounded CPU sample: the four M=16 calls of the workload (one per projection shape)."""
+    picked = [c for c in wl.cases(1) if c.m == 16]
+    return picked, [wl.make_inputs(c, device="cpu") for c in picked]
+
+
+def cpu_baseline(torch, wl):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cpu_baseline as port  # the oracle's timed leg; the only use of oracle/ in this file
+
+    picked, inputs = cpu_sample(torch, wl)
+    seconds = port.time_cases(inputs, repeats=2)
+    nbytes = sum(c.algorithmic_bytes() for c in picked)
+    return {"value": round(nbytes / seconds / 1e12, 6), "unit": UNIT, "cores": port.host_threads(), "kind": "port",
+            "sample": "the four M=16 calls of the workload once (218 MB of weights), dequantise + fp32 matmul, "
+                      "torch CPU, best of 2"}
+
+
+def run_reference(args):
+    """The reference's semantics on the host cores (it has no CUDA path and no CPU code of its own
+    for this op; oracle/cpu_baseline.py ports reference.py:18-25 + wrapped.py:115)."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import torch
+
+    from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cpu_baseline as port
+
+    picked, inputs = cpu_sample(torch, wl)
+    nbytes = sum(c.algorithmic_bytes() for c in picked)
+    torch.set_num_threads(port.host_threads())
+    for _ in range(max(args.warmup, 1)):
+        port.time_cases(inputs, repeats=0)
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        for inp in inputs:
+            port.skinny_gemm_cpu(inp["a"], inp["w"], inp["scale"], inp["d_in"])
+    seconds = time.perf_counter() - start
+    ms_per_step = seconds / args.steps * 1e3
+    value = nbytes / (ms_per_step * 1e-3) / 1e12
+    sample = "each step = the four M=16 calls of the workload (218 MB of weights) on the host cores"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 6), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(ms_per_step, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 out)",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": round(value, 6), "unit": UNIT, "cores": port.host_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 6), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--no-detail", action="store_true", help="skip the per-case table")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

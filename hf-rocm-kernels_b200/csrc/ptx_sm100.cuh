@@ -188,6 +188,35 @@ __device__ __forceinline__ float dsmem_ld_f32(uint32_t cluster_addr) {
     return v;
 }
 
+// Split cluster barrier: arrive early (non-blocking), wait later.
+__device__ __forceinline__ void cluster_arrive_release() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_wait_acquire() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Bulk copy from this CTA's shared memory into a peer's (addresses from dsmem_map); the bytes
+// are counted on the PEER's mbarrier. Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void dsmem_bulk_copy(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
+                                                uint32_t peer_bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(peer_bar_cluster_addr)
+        : "memory");
+}
+
+// The issuing thread's bulk copies have finished READING their source.
+__device__ __forceinline__ void bulk_copies_source_done() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // Both are no-ops when the grid was launched without the programmatic-serialisation attribute.
 __device__ __forceinline__ void pdl_wait_prior_grids() {

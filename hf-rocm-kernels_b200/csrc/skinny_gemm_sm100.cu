@@ -47,6 +47,7 @@ struct Ctrl {
     uint64_t full[kMaxStages];    // TMA -> MMA : stage holds data
     uint64_t empty[kMaxStages];   // MMA -> TMA : stage may be overwritten
     uint64_t accum;               // MMA -> epilogue : accumulator complete
+    uint64_t recv;                // peers -> this CTA : split-K partials landed (byte count)
     uint32_t tmem_base;
     volatile uint32_t abort;      // set by the first role whose wait ran out
 };
@@ -90,6 +91,11 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const uint32_t full_bar = smem_u32(&ctrl->full[0]);
     const uint32_t empty_bar = smem_u32(&ctrl->empty[0]);
     const uint32_t accum_bar = smem_u32(&ctrl->accum);
+    const uint32_t recv_bar = smem_u32(&ctrl->recv);
+    // Split-K reduction geometry: the m x 128 tile is cut into `split` element ranges of `chunk`
+    // floats (a multiple of 4, so that every range is a 16-byte-aligned bulk copy).
+    const int total = p.m * kTileN;
+    const uint32_t chunk = ((static_cast<uint32_t>(total) + p.split - 1) / p.split + 3u) & ~3u;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -117,7 +123,9 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 mbar_init(empty_bar + 8u * s, 1);
             }
             mbar_init(accum_bar, 1);
+            mbar_init(recv_bar, 1);
             mbar_init_fence();
+            if (p.split > 1) mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>(p.split) * chunk * 4u);
         }
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"r"(kThreads) : "memory");
@@ -151,6 +159,9 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         tcgen05_fence_after_sync();
     }
     pdl_launch_dependents();
+    // Every CTA of the cluster has initialised its barriers once this cluster barrier completes;
+    // it is only waited for much later, right before partials are pushed to the peers.
+    if (p.split > 1) cluster_arrive_release();
     const uint32_t tmem_acc = ctrl->tmem_base;
     if (threadIdx.x == 0) stamp(p, 1);
 
@@ -205,8 +216,20 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             stamp(p, 4);
         }
         __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ epilogue (warps 0..3)
+    }
+
+    // ---------------------------------------------------------------------- epilogue (warps 0..3)
+    // split == 1: each thread owns one W row (= output column) and writes D straight from TMEM.
+    // split  > 1: every CTA of the cluster owns one `chunk` of the tile. A CTA stages its partial
+    // tile in its own shared memory and sends range q to CTA q with one bulk shared-to-shared copy
+    // that counts bytes on q's `recv` barrier; an owner waits (bounded) until all `split` ranges
+    // have landed, adds them in rank order out of its own memory and writes D. No cluster-wide
+    // barrier sits on this path; the one issued at start-up only proves the peers' barriers exist.
+    constexpr int kOwned = 8;  // owned elements per thread kept in registers (covers m <= 16)
+    const bool epilogue_warp = warp < kEpilogueThreads / 32;
+    const uint32_t recv_addr = smem_u32(ctrl) + kCtrlBytes;  // float recv[split][chunk]
+    if (p.split > 1 && !epilogue_warp) cluster_wait_acquire();
+    if (epilogue_warp) {
         pdl_wait_prior_grids();
         const int nl = threadIdx.x;  // TMEM lane = W row inside the tile
         const int n = n0 + nl;
@@ -214,6 +237,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const float scale = __ldg(p.scale) * p.kind_factor;
         const uint32_t lane_taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
 
+        // D_in is requested long before it is needed.
         float din[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -221,14 +245,24 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                          ? load_out(p.d, static_cast<size_t>(j) * p.n + n, p.d_dtype)
                          : 0.0f;
         }
+        float d_own[kOwned];
+#pragma unroll
+        for (int it = 0; it < kOwned; ++it) {
+            const uint32_t off = threadIdx.x + it * kEpilogueThreads;
+            const int e = static_cast<int>(rank * chunk + off);
+            const int col = n0 + (e % kTileN);
+            d_own[it] = (!direct && p.accumulate && off < chunk && e < total && col < p.n)
+                            ? load_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype)
+                            : 0.0f;
+        }
 
         bool ok = mbar_wait_bounded(accum_bar, 0u, &ctrl->abort, kRoleEpilogue);
         ok = __all_sync(0xffffffffu, ok) && ctrl->abort == 0u;
         ok = __all_sync(0xffffffffu, ok);
         if (threadIdx.x == 0) stamp(p, 5);
         tcgen05_fence_after_sync();
+        float* const partial = reinterpret_cast<float*>(ring_ptr);  // the ring is idle by now
         if (ok) {
-            float* const partial = reinterpret_cast<float*>(ring_ptr);
             for (int c = 0; c < p.m_pad / 16; ++c) {
                 uint32_t v[16];
                 tmem_ld_32x32b_x16(lane_taddr + static_cast<uint32_t>(c * 16), v);
@@ -246,77 +280,59 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        partial[(c * 16 + j) * kTileN + nl] = __uint_as_float(v[j]);
+                        const int m = c * 16 + j;
+                        if (m < p.m) partial[m * kTileN + nl] = __uint_as_float(v[j]);
                     }
                 }
             }
         }
-    }
-
-    if (p.split > 1) {
-        // Reduce-scatter of the split-K partial tiles through distributed shared memory: CTA `rank`
-        // finalises elements [rank*chunk, (rank+1)*chunk) of the m x 128 tile, reading every peer's
-        // copy (its own included) in rank order.
-        constexpr int kPrefetch = 8;
-        const int total = p.m * kTileN;
-        const int chunk = (total + p.split - 1) / p.split;
-        const int e_begin = rank * chunk;
-        const int e_end = e_begin + chunk < total ? e_begin + chunk : total;
-        const bool reducer = warp < kEpilogueThreads / 32;
-        // Nothing may be outstanding in global memory here: the release half of the barrier would
-        // wait for it. D_in is therefore requested after the barrier, together with the peers' data.
-        cluster_sync_all();
-        float d_in[kPrefetch];
-        if (reducer) {
-#pragma unroll
-            for (int it = 0; it < kPrefetch; ++it) {
-                const int e = e_begin + static_cast<int>(threadIdx.x) + it * kEpilogueThreads;
-                const int n = n0 + (e % kTileN);
-                d_in[it] = (p.accumulate && e < e_end && n < p.n)
-                               ? load_out(p.d, static_cast<size_t>(e / kTileN) * p.n + n, p.d_dtype)
-                               : 0.0f;
-            }
-        }
-        if (reducer && ctrl->abort == 0u) {
-            const float scale = __ldg(p.scale) * p.kind_factor;
-#pragma unroll
-            for (int it = 0; it < kPrefetch; ++it) {
-                const int e = e_begin + static_cast<int>(threadIdx.x) + it * kEpilogueThreads;
-                if (e < e_end) {
-                    // All peers' values are requested before the first one is consumed.
-                    float v[kMaxSplit];
-#pragma unroll
-                    for (int q = 0; q < kMaxSplit; ++q) {
-                        v[q] = q < p.split ? dsmem_ld_f32(dsmem_map(ring_addr + 4u * static_cast<uint32_t>(e),
-                                                                    static_cast<uint32_t>(q)))
-                                           : 0.0f;
-                    }
-                    float sum = 0.0f;
-#pragma unroll
-                    for (int q = 0; q < kMaxSplit; ++q) sum += v[q];
-                    const int n = n0 + (e % kTileN);
-                    if (n < p.n) {
-                        store_out(p.d, static_cast<size_t>(e / kTileN) * p.n + n, p.d_dtype,
-                                  fmaf(sum, scale, d_in[it]));
-                    }
-                }
-            }
-            // Token counts above 16 leave more than kPrefetch elements per thread for small splits.
-            for (int e = e_begin + static_cast<int>(threadIdx.x) + kPrefetch * kEpilogueThreads; e < e_end;
-                 e += kEpilogueThreads) {
-                float sum = 0.0f;
+        if (!direct) {
+            // generic-proxy writes above -> visible to the bulk-copy engine, then one thread sends
+            fence_proxy_async_smem();
+            cluster_wait_acquire();
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+            if (threadIdx.x == 0 && ok) {
                 for (int q = 0; q < p.split; ++q) {
-                    sum += dsmem_ld_f32(dsmem_map(ring_addr + 4u * static_cast<uint32_t>(e), static_cast<uint32_t>(q)));
-                }
-                const int n = n0 + (e % kTileN);
-                if (n < p.n) {
-                    const size_t idx = static_cast<size_t>(e / kTileN) * p.n + n;
-                    const float d0 = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
-                    store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d0));
+                    dsmem_bulk_copy(dsmem_map(recv_addr + 4u * rank * chunk, static_cast<uint32_t>(q)),
+                                    ring_addr + 4u * static_cast<uint32_t>(q) * chunk, 4u * chunk,
+                                    dsmem_map(recv_bar, static_cast<uint32_t>(q)));
                 }
             }
+            bool landed = ok && mbar_wait_bounded(recv_bar, 0u, &ctrl->abort, kRoleEpilogue);
+            landed = __all_sync(0xffffffffu, landed);
+            if (landed) {
+                const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
+#pragma unroll
+                for (int it = 0; it < kOwned; ++it) {
+                    const uint32_t off = threadIdx.x + it * kEpilogueThreads;
+                    const int e = static_cast<int>(rank * chunk + off);
+                    if (off < chunk && e < total) {
+                        float sum = 0.0f;
+                        for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + off];
+                        const int col = n0 + (e % kTileN);
+                        if (col < p.n) {
+                            store_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype,
+                                      fmaf(sum, scale, d_own[it]));
+                        }
+                    }
+                }
+                // token counts above 16 own more than kOwned elements per thread for small splits
+                for (uint32_t off = threadIdx.x + kOwned * kEpilogueThreads; off < chunk; off += kEpilogueThreads) {
+                    const int e = static_cast<int>(rank * chunk + off);
+                    if (e >= total) break;
+                    float sum = 0.0f;
+                    for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + off];
+                    const int col = n0 + (e % kTileN);
+                    if (col < p.n) {
+                        const size_t idx = static_cast<size_t>(e / kTileN) * p.n + col;
+                        const float d0 = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
+                        store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d0));
+                    }
+                }
+            }
+            // the staged partial tile must outlive the copies that read it
+            if (threadIdx.x == 0) bulk_copies_source_done();
         }
-        cluster_sync_relaxed();  // no CTA leaves while a peer may still read its shared memory
     }
 
     if (threadIdx.x == 0) stamp(p, 6);
@@ -419,11 +435,15 @@ int round_up(int v, int to) { return (v + to - 1) / to * to; }
 
 // Launch shape of the cluster kernel for one launch of m <= kMaxMPad tokens, from sweeps on B200
 // (148 SMs) over the Llama-3 8B/70B projection shapes:
-//   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream; with fewer
-//     tiles than SMs the K split is chosen so that tiles * split comes to about two CTAs per SM;
-//   * short rings and many CTAs beat long rings and few: three co-resident CTAs of four 18 KiB
-//     stages hide each other's fill, drain and reduction better than one CTA with twelve stages;
-//   * a split never gets fewer than four K blocks (it would be all pipeline fill).
+//   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream, and several
+//     small CTAs per SM hide each other's fill, drain and reduction better than one big one:
+//     with a K split the ring is sized so that THREE CTAs fit an SM (3 stages of 18 KiB at
+//     16 tokens, 4 at a single token, whose receive buffer is tiny);
+//   * the whole grid must be resident at once. A cluster that has to wait for a free slot starts
+//     late and then streams alone at a fraction of the bandwidth, which costs far more than a
+//     slightly uneven spread: the split is the largest one (up to 8, or 16 for very narrow
+//     matrices) that keeps tiles * split within 3 * 148 CTAs, with at least two K blocks each;
+//   * without a split (tiles alone cover the SMs) a deeper ring and two CTAs per SM are best.
 int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
     if (split_req < 0 || split_req > kMaxSplit || stages_req < 0 || stages_req == 1 || stages_req > kMaxStages)
@@ -432,20 +452,33 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     const int tiles = (n + kTileN - 1) / kTileN;
     const int nkb = (k + kBlockK - 1) / kBlockK;
     const int stage_bytes = kWStageBytes + m_pad * kBlockK;
-    const int max_stages_fit = (kSmemLimit - 1024 - kCtrlBytes) / stage_bytes;
+    constexpr int kCtasPerSmSplit = 3;
+    constexpr int kResident = kCtasPerSmSplit * kNumSms;
 
     int split = split_req;
     if (split == 0) {
-        split = 1;
-        if (tiles < kNumSms) {
-            split = (2 * kNumSms + tiles / 2) / tiles;
-            if (split > 8) split = 8;
-            while (split > 1 && nkb / split < 4) --split;
-        }
+        split = kResident / tiles;
+        const int cap = tiles * 8 < kNumSms ? kMaxSplit : 8;
+        if (split > cap) split = cap;
+        if (split > nkb / 2) split = nkb / 2;
+        if (split < 1) split = 1;
     }
     if (split > nkb) split = nkb;
 
-    int stages = stages_req != 0 ? stages_req : (split > 1 ? 4 : 6);
+    const int chunk = (((m * kTileN + split - 1) / split) + 3) & ~3;
+    const int recv_bytes = split > 1 ? split * chunk * 4 : 0;
+    const int fixed_bytes = 1024 + kCtrlBytes + recv_bytes;
+    const int max_stages_fit = (kSmemLimit - fixed_bytes) / stage_bytes;
+    int stages = stages_req;
+    if (stages == 0) {
+        if (split > 1) {
+            const int per_cta = 228 * 1024 / kCtasPerSmSplit - 1024;
+            stages = (per_cta - fixed_bytes) / stage_bytes;
+            if (stages < 2) stages = 2;
+        } else {
+            stages = 6;
+        }
+    }
     if (stages > max_stages_fit) stages = max_stages_fit;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return HFRK_INVALID_CONFIG;
@@ -453,7 +486,7 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     plan->split = split;
     plan->stages = stages;
     plan->ctas = tiles * split;
-    plan->smem_bytes = 1024 + stages * stage_bytes + kCtrlBytes;
+    plan->smem_bytes = fixed_bytes + stages * stage_bytes;
     plan->m_pad = m_pad;
     plan->num_kblocks = nkb;
     return HFRK_SUCCESS;
