@@ -28,7 +28,7 @@ constexpr int kNumSms = 148;
 constexpr int kCtrlBytes = 256;                     // shared-memory control block after the ring
 constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds of SM clock
 
-enum Role : int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3 };
+enum Role : int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3, kRolePeer = 4 };
 
 // Device-side status of this library on the current device. Written only when a bounded wait
 // runs out; read and cleared by hfrk_device_status().
@@ -65,12 +65,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 
 __device__ __forceinline__ float load_out(const void* d, size_t idx, int dtype) {
+    if (dtype == HFRK_F32) return static_cast<const float*>(d)[idx];
     return dtype == HFRK_BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(d)[idx])
                               : __half2float(static_cast<const __half*>(d)[idx]);
 }
 
 __device__ __forceinline__ void store_out(void* d, size_t idx, int dtype, float v) {
-    if (dtype == HFRK_BF16) {
+    if (dtype == HFRK_F32) {
+        static_cast<float*>(d)[idx] = v;
+    } else if (dtype == HFRK_BF16) {
         static_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
     } else {
         static_cast<__half*>(d)[idx] = __float2half_rn(v);

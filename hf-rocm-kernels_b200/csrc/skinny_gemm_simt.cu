@@ -95,7 +95,7 @@ extern "C" int hfrk_skinny_gemm_fp8_simt(const void* A, const void* W, void* D, 
         return HFRK_INVALID_CONFIG;
     if ((a_kind != HFRK_E4M3FN && a_kind != HFRK_E4M3FNUZ) || (w_kind != HFRK_E4M3FN && w_kind != HFRK_E4M3FNUZ) ||
         (d_dtype != HFRK_F16 && d_dtype != HFRK_BF16))
-        return HFRK_BAD_DTYPE;
+        return HFRK_BAD_DTYPE;  // the diagnostic kernel has no fp32 output
     if (k % 16 != 0) return HFRK_K_NOT_DIVISIBLE;
     if (w_row_stride < k || w_row_stride % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) ||
         (reinterpret_cast<uintptr_t>(W) & 15u))

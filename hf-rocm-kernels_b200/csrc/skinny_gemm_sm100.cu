@@ -53,6 +53,21 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
 
+// Row-parallel (K split over GPUs) exchange state, as seen by the kernel of ONE rank. Every rank
+// owns an exchange buffer that its peers write into over NVLink:
+//   data  : float [2 parities][world sources][elems_per_src]   partial sums, fp32
+//   flags : u32   [2 parities][world sources][flags_per_src]   epoch numbers, one per (tile, K-split rank)
+// data[p] / flags[p] are the bases of rank p's buffer (p == rank: the local one).
+constexpr int kMaxWorld = 8;
+struct RowparDev {
+    int rank, world;
+    unsigned int elems_per_src, flags_per_src;
+    float* data[kMaxWorld];
+    unsigned int* flags[kMaxWorld];
+    unsigned int* call_index;   // local: number of completed calls on this communicator
+    unsigned int* done_ctas;    // local: CTAs of the running call that have finished
+};
+
 struct GemmParams {
     void* d;
     const float* scale;
@@ -65,6 +80,7 @@ struct GemmParams {
     int d_dtype;
     int accumulate;
     unsigned long long* stamps;  // optional [cta][8] globaltimer samples (diagnostic entry point only)
+    RowparDev rp;                // used by the row-parallel instantiation only
 };
 
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
@@ -77,7 +93,118 @@ __device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
     }
 }
 
-__global__ void __launch_bounds__(kThreads)
+
+// ---------------------------------------------------------------- cross-GPU exchange (row-parallel)
+__device__ __forceinline__ void st_release_sys(unsigned int* ptr, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* ptr) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* ptr) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
+// AND of a predicate over the 128 epilogue threads (named barrier 1 with reduction).
+__device__ __forceinline__ bool epilogue_vote_all(bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pin, pout;\n\t"
+        "setp.ne.u32 pin, %1, 0;\n\t"
+        "barrier.cta.red.and.pred pout, 1, %2, pin;\n\t"
+        "selp.u32 %0, 1, 0, pout;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "r"(pred ? 1u : 0u), "r"(kEpilogueThreads)
+        : "memory");
+    return out != 0;
+}
+
+// One-shot all-reduce of the values the 128 epilogue threads of this CTA own, fused into the GEMM
+// epilogue. Each thread holds CNT partial sums (`val`), `slot[i]` is the element's index in the
+// exchange buffer (0xffffffff = unused). The CTA writes its partials into every peer's buffer
+// (plain stores to peer memory: NVLink), publishes one epoch-valued flag per peer, waits (bounded)
+// for the matching flag of every peer, and adds the `world` contributions in rank order, so that
+// all ranks compute bit-identical sums. Returns false if a peer did not show up in time.
+template <int CNT>
+__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, unsigned int flag_slot,
+                                                const uint32_t (&slot)[CNT], float (&val)[CNT],
+                                                volatile uint32_t* abort_flag) {
+    const unsigned int parity = epoch & 1u;
+    const size_t my_src = static_cast<size_t>(parity * rp.world + rp.rank);
+    for (int peer = 0; peer < rp.world; ++peer) {
+        if (peer == rp.rank) continue;
+        float* dst = rp.data[peer] + my_src * rp.elems_per_src;
+#pragma unroll
+        for (int i = 0; i < CNT; ++i) {
+            if (slot[i] != 0xffffffffu) dst[slot[i]] = val[i];
+        }
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+    bool ok = true;
+    const int t = static_cast<int>(threadIdx.x);
+    if (t < rp.world && t != rp.rank) {
+        st_release_sys(rp.flags[t] + my_src * rp.flags_per_src + flag_slot, epoch);
+        const unsigned int* mine = rp.flags[rp.rank] + static_cast<size_t>(parity * rp.world + t) * rp.flags_per_src + flag_slot;
+        const long long start = clock64();
+        while (ld_acquire_sys(mine) != epoch) {
+            if (*abort_flag || clock64() - start > kWaitLimitCycles) {
+                *abort_flag = 1u;
+                record_timeout(kRolePeer);
+                ok = false;
+                break;
+            }
+        }
+    }
+    ok = epilogue_vote_all(ok);
+    if (!ok) return false;
+    // Loads are issued a batch at a time (4 elements x up to 7 peers in flight per thread); batches
+    // whose elements are all unused are skipped, which is the common case: a thread usually owns
+    // two or three elements of the tile.
+    constexpr int kBatch = 4;
+#pragma unroll
+    for (int i0 = 0; i0 < CNT; i0 += kBatch) {
+        bool any = false;
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) any |= slot[i0 + b] != 0xffffffffu;
+        if (!any) continue;
+        float got[kBatch][kMaxWorld];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+#pragma unroll
+            for (int src = 0; src < kMaxWorld; ++src) {
+                got[b][src] = 0.0f;
+                if (src < rp.world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
+                    got[b][src] = ld_relaxed_sys_f32(rp.data[rp.rank] +
+                                                     static_cast<size_t>(parity * rp.world + src) * rp.elems_per_src +
+                                                     slot[i0 + b]);
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int src = 0; src < kMaxWorld; ++src) {
+                if (src < rp.world) sum += (src == rp.rank) ? val[i0 + b] : got[b][src];
+            }
+            val[i0 + b] = sum;
+        }
+    }
+    return true;
+}
+
+// kRowPar: the epilogue all-reduces the tile over the ranks of a row-parallel group before D is written.
+template <bool kRowPar>
+__global__ void __launch_bounds__(kThreads, kRowPar ? 3 : 1)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -236,6 +363,10 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const bool direct = p.split == 1;
         const float scale = __ldg(p.scale) * p.kind_factor;
         const uint32_t lane_taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
+        // Row-parallel: the call's epoch (completed calls + 1) and this tile's place in the exchange buffer.
+        unsigned int epoch = 0;
+        if (kRowPar) epoch = *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
+        const uint32_t tile_slot0 = blockIdx.x * static_cast<uint32_t>(total);
 
         // D_in is requested long before it is needed.
         float din[16];
@@ -259,6 +390,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         bool ok = mbar_wait_bounded(accum_bar, 0u, &ctrl->abort, kRoleEpilogue);
         ok = __all_sync(0xffffffffu, ok) && ctrl->abort == 0u;
         ok = __all_sync(0xffffffffu, ok);
+        if (kRowPar) ok = epilogue_vote_all(ok);  // the exchange below contains CTA-wide barriers
         if (threadIdx.x == 0) stamp(p, 5);
         tcgen05_fence_after_sync();
         float* const partial = reinterpret_cast<float*>(ring_ptr);  // the ring is idle by now
@@ -268,10 +400,23 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 tmem_ld_32x32b_x16(lane_taddr + static_cast<uint32_t>(c * 16), v);
                 tmem_ld_wait();
                 if (direct) {
+                    if (kRowPar) {
+                        // host guarantees m <= 16 here: one chunk, 16 values per thread
+                        float val[16];
+                        uint32_t slot[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            val[j] = __uint_as_float(v[j]);
+                            slot[j] = j < p.m ? tile_slot0 + static_cast<uint32_t>(j * kTileN + nl) : 0xffffffffu;
+                        }
+                        if (!rowpar_exchange<16>(p.rp, epoch, blockIdx.x * kMaxSplit, slot, val, &ctrl->abort)) ok = false;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(val[j]);
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = c * 16 + j;
-                        if (m < p.m && n < p.n) {
+                        if (ok && m < p.m && n < p.n) {
                             const size_t idx = static_cast<size_t>(m) * p.n + n;
                             const float d_in = c == 0 ? din[j] : (p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f);
                             store_out(p.d, idx, p.d_dtype, fmaf(__uint_as_float(v[j]), scale, d_in));
@@ -300,19 +445,34 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
             bool landed = ok && mbar_wait_bounded(recv_bar, 0u, &ctrl->abort, kRoleEpilogue);
             landed = __all_sync(0xffffffffu, landed);
+            if (kRowPar) landed = epilogue_vote_all(landed);
             if (landed) {
                 const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
+                float own[kOwned];
+                uint32_t slot[kOwned];
 #pragma unroll
                 for (int it = 0; it < kOwned; ++it) {
                     const uint32_t off = threadIdx.x + it * kEpilogueThreads;
                     const int e = static_cast<int>(rank * chunk + off);
+                    float sum = 0.0f;
                     if (off < chunk && e < total) {
-                        float sum = 0.0f;
                         for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + off];
+                    }
+                    own[it] = sum;
+                    slot[it] = (off < chunk && e < total) ? tile_slot0 + static_cast<uint32_t>(e) : 0xffffffffu;
+                }
+                if (kRowPar) {
+                    landed = rowpar_exchange<kOwned>(p.rp, epoch, blockIdx.x * kMaxSplit + rank, slot, own, &ctrl->abort);
+                }
+#pragma unroll
+                for (int it = 0; it < kOwned; ++it) {
+                    const uint32_t off = threadIdx.x + it * kEpilogueThreads;
+                    const int e = static_cast<int>(rank * chunk + off);
+                    if (landed && off < chunk && e < total) {
                         const int col = n0 + (e % kTileN);
                         if (col < p.n) {
                             store_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype,
-                                      fmaf(sum, scale, d_own[it]));
+                                      fmaf(own[it], scale, d_own[it]));
                         }
                     }
                 }
@@ -339,6 +499,17 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kMmaWarp) tmem_dealloc(tmem_acc, tmem_cols);
+    if (kRowPar && threadIdx.x == 0) {
+        // The last CTA of the grid closes the call: every CTA has read the call index by now.
+        __threadfence();
+        const unsigned int ctas = gridDim.x * gridDim.y;
+        if (atomicAdd(p.rp.done_ctas, 1u) == ctas - 1u) {
+            *p.rp.done_ctas = 0u;
+            *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) =
+                *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
+            __threadfence();
+        }
+    }
     if (threadIdx.x == 0) stamp(p, 7);
 }
 
@@ -499,9 +670,12 @@ int prepare_device_once() {
     HFRK_CUDA_TRY(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && done[dev]) return HFRK_SUCCESS;
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemLimit));
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemLimit));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<1>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<2>,
@@ -516,11 +690,12 @@ int validate(const void* A, const void* W, void* D, const float* scale_dev, int 
     if (m <= 0 || n <= 0 || k <= 0) return HFRK_INVALID_CONFIG;
     if ((a_kind != HFRK_E4M3FN && a_kind != HFRK_E4M3FNUZ) || (w_kind != HFRK_E4M3FN && w_kind != HFRK_E4M3FNUZ))
         return HFRK_BAD_DTYPE;
-    if (d_dtype != HFRK_F16 && d_dtype != HFRK_BF16) return HFRK_BAD_DTYPE;
+    if (d_dtype != HFRK_F16 && d_dtype != HFRK_BF16 && d_dtype != HFRK_F32) return HFRK_BAD_DTYPE;
     if (k % 16 != 0) return HFRK_K_NOT_DIVISIBLE;
     if (w_row_stride < k || w_row_stride % 16 != 0) return HFRK_BAD_ALIGNMENT;
     if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) ||
-        (reinterpret_cast<uintptr_t>(D) & 1u) || (reinterpret_cast<uintptr_t>(scale_dev) & 3u))
+        (reinterpret_cast<uintptr_t>(D) & (d_dtype == HFRK_F32 ? 3u : 1u)) ||
+        (reinterpret_cast<uintptr_t>(scale_dev) & 3u))
         return HFRK_BAD_ALIGNMENT;
     return HFRK_SUCCESS;
 }
@@ -647,7 +822,7 @@ int launch_streamk(const void* A, const void* W, void* D, const float* scale_dev
         if (rc != HFRK_SUCCESS) return rc;
 
         SkParams p;
-        p.d = static_cast<uint8_t*>(D) + static_cast<size_t>(m0) * n * 2;
+        p.d = static_cast<uint8_t*>(D) + static_cast<size_t>(m0) * n * (d_dtype == HFRK_F32 ? 4 : 2);
         p.scale = scale_dev;
         p.kind_factor = (a_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f) * (w_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f);
         p.m = mc;
@@ -689,13 +864,14 @@ int launch_streamk(const void* A, const void* W, void* D, const float* scale_dev
 int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, int m, int n, int k,
                 int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int variant,
                 int split_req, int ctas_per_sm, int stages_req, int use_pdl, cudaStream_t stream,
-                unsigned long long* stamps = nullptr) {
+                unsigned long long* stamps = nullptr, const RowparDev* rowpar = nullptr) {
     int rc = validate(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype);
     if (rc != HFRK_SUCCESS) return rc;
     rc = prepare_device_once();
     if (rc != HFRK_SUCCESS) return rc;
     if (variant < HFRK_VARIANT_AUTO || variant > HFRK_VARIANT_STREAMK) return HFRK_INVALID_CONFIG;
     if (variant == HFRK_VARIANT_AUTO) variant = HFRK_VARIANT_CLUSTER;
+    if (rowpar != nullptr && variant != HFRK_VARIANT_CLUSTER) return HFRK_INVALID_CONFIG;
     if (variant == HFRK_VARIANT_STREAMK) {
         return launch_streamk(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
                               ctas_per_sm, stages_req, use_pdl, stream, stamps);
@@ -706,9 +882,11 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
                         kTileN, &tmap_w);
     if (rc != HFRK_SUCCESS) return rc;
 
-    const size_t out_elem = 2;
-    for (int m0 = 0; m0 < m; m0 += kMaxMPad) {
-        const int mc = m - m0 < kMaxMPad ? m - m0 : kMaxMPad;
+    const size_t out_elem = d_dtype == HFRK_F32 ? 4 : 2;
+    // the fused all-reduce keeps a thread's share of the tile in registers: 16 tokens per launch
+    const int m_step = rowpar != nullptr ? 16 : kMaxMPad;
+    for (int m0 = 0; m0 < m; m0 += m_step) {
+        const int mc = m - m0 < m_step ? m - m0 : m_step;
         Plan plan;
         rc = make_plan(mc, n, k, split_req, stages_req, &plan);
         if (rc != HFRK_SUCCESS) return rc;
@@ -732,6 +910,14 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         p.d_dtype = d_dtype;
         p.accumulate = accumulate ? 1 : 0;
         p.stamps = stamps;
+        memset(&p.rp, 0, sizeof(p.rp));
+        if (rowpar != nullptr) {
+            p.rp = *rowpar;
+            const unsigned tiles = static_cast<unsigned>((n + kTileN - 1) / kTileN);
+            if (static_cast<unsigned long long>(tiles) * mc * kTileN > p.rp.elems_per_src ||
+                tiles * kMaxSplit > p.rp.flags_per_src)
+                return HFRK_TOO_LARGE;
+        }
 
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
@@ -755,13 +941,131 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         }
         cfg.attrs = attrs;
         cfg.numAttrs = num_attrs;
-        HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel, tmap_w, tmap_a, p));
+        if (rowpar != nullptr) {
+            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<true>, tmap_w, tmap_a, p));
+        } else {
+            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<false>, tmap_w, tmap_a, p));
+        }
     }
     return HFRK_SUCCESS;
 }
 
 }  // namespace
 }  // namespace hfrk
+
+
+// =============================================================================== row-parallel group
+struct hfrk_rowpar {
+    hfrk::RowparDev dev;
+    uint8_t* local_block = nullptr;
+    size_t block_bytes = 0;
+    size_t flags_offset = 0;
+    void* opened[hfrk::kMaxWorld] = {};   // peer mappings opened from IPC handles
+    int device = 0;
+    bool connected = false;
+};
+
+namespace hfrk {
+namespace {
+
+size_t rowpar_data_bytes(int world, unsigned elems_per_src) { return static_cast<size_t>(2) * world * elems_per_src * 4; }
+size_t rowpar_flag_bytes(int world, unsigned flags_per_src) { return static_cast<size_t>(2) * world * flags_per_src * 4; }
+
+void rowpar_point(hfrk_rowpar* g, int peer, uint8_t* base) {
+    g->dev.data[peer] = reinterpret_cast<float*>(base);
+    g->dev.flags[peer] = reinterpret_cast<unsigned int*>(base + g->flags_offset);
+}
+
+}  // namespace
+}  // namespace hfrk
+
+extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out) {
+    if (out == nullptr || world < 1 || world > hfrk::kMaxWorld || rank < 0 || rank >= world || max_m < 1 ||
+        max_n < 1)
+        return HFRK_BAD_WORLD;
+    const int tiles = (max_n + hfrk::kTileN - 1) / hfrk::kTileN;
+    const int m_cap = max_m < 16 ? max_m : 16;  // larger M runs as launches of 16 tokens
+    hfrk_rowpar* g = new hfrk_rowpar();
+    g->dev.rank = rank;
+    g->dev.world = world;
+    g->dev.elems_per_src = static_cast<unsigned>(tiles) * m_cap * hfrk::kTileN;
+    g->dev.flags_per_src = static_cast<unsigned>(tiles) * hfrk::kMaxSplit;
+    const size_t data = (hfrk::rowpar_data_bytes(world, g->dev.elems_per_src) + 255) / 256 * 256;
+    const size_t flags = (hfrk::rowpar_flag_bytes(world, g->dev.flags_per_src) + 255) / 256 * 256;
+    g->flags_offset = data;
+    g->block_bytes = data + flags + 256;
+    cudaError_t err = cudaGetDevice(&g->device);
+    if (err == cudaSuccess) err = cudaMalloc(&g->local_block, g->block_bytes);
+    if (err == cudaSuccess) err = cudaMemset(g->local_block, 0, g->block_bytes);
+    if (err != cudaSuccess) {
+        hfrk::set_last_error(cudaGetErrorString(err));
+        (void)cudaGetLastError();
+        delete g;
+        return HFRK_CUDA_ERROR;
+    }
+    hfrk::rowpar_point(g, rank, g->local_block);
+    g->dev.call_index = reinterpret_cast<unsigned int*>(g->local_block + data + flags);
+    g->dev.done_ctas = g->dev.call_index + 1;
+    g->connected = world == 1;
+    *out = g;
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_rowpar_ipc_handle(hfrk_rowpar* g, void* handle64_out) {
+    if (g == nullptr || handle64_out == nullptr) return HFRK_BAD_WORLD;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t handle;
+    HFRK_CUDA_TRY(cudaIpcGetMemHandle(&handle, g->local_block));
+    memcpy(handle64_out, &handle, sizeof(handle));
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_rowpar_connect(hfrk_rowpar* g, const void* all_handles) {
+    if (g == nullptr || all_handles == nullptr) return HFRK_BAD_WORLD;
+    for (int peer = 0; peer < g->dev.world; ++peer) {
+        if (peer == g->dev.rank) continue;
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, static_cast<const uint8_t*>(all_handles) + 64 * peer, sizeof(handle));
+        void* mapped = nullptr;
+        HFRK_CUDA_TRY(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
+        g->opened[peer] = mapped;
+        hfrk::rowpar_point(g, peer, static_cast<uint8_t*>(mapped));
+    }
+    g->connected = true;
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_rowpar_connect_pointers(hfrk_rowpar* g, void* const* peer_blocks) {
+    if (g == nullptr || peer_blocks == nullptr) return HFRK_BAD_WORLD;
+    for (int peer = 0; peer < g->dev.world; ++peer) {
+        if (peer == g->dev.rank) continue;
+        if (peer_blocks[peer] == nullptr) return HFRK_BAD_WORLD;
+        hfrk::rowpar_point(g, peer, static_cast<uint8_t*>(peer_blocks[peer]));
+    }
+    g->connected = true;
+    return HFRK_SUCCESS;
+}
+
+extern "C" void* hfrk_rowpar_local_block(hfrk_rowpar* g) { return g == nullptr ? nullptr : g->local_block; }
+
+extern "C" int hfrk_rowpar_destroy(hfrk_rowpar* g) {
+    if (g == nullptr) return HFRK_SUCCESS;
+    for (int peer = 0; peer < hfrk::kMaxWorld; ++peer) {
+        if (g->opened[peer] != nullptr) (void)cudaIpcCloseMemHandle(g->opened[peer]);
+    }
+    if (g->local_block != nullptr) (void)cudaFree(g->local_block);
+    delete g;
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* g, const void* A, const void* W, void* D,
+                                           const float* scale_dev, int m, int n, int k_shard, int64_t w_row_stride,
+                                           int a_kind, int w_kind, int d_dtype, int accumulate, void* stream) {
+    if (g == nullptr || !g->connected) return HFRK_BAD_WORLD;
+    return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k_shard, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
+                             HFRK_VARIANT_CLUSTER, 0, 0, 0, hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream),
+                             nullptr, &g->dev);
+}
 
 // =============================================================================== C ABI
 
@@ -796,7 +1100,7 @@ extern "C" int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* 
 extern "C" int64_t hfrk_host_call_workspace_bytes(int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0) return 0;
     const int64_t a_bytes = (static_cast<int64_t>(m) * k + 255) / 256 * 256;
-    const int64_t d_bytes = (static_cast<int64_t>(m) * n * 2 + 255) / 256 * 256;
+    const int64_t d_bytes = (static_cast<int64_t>(m) * n * 4 + 255) / 256 * 256;
     return a_bytes + d_bytes;
 }
 
@@ -808,7 +1112,7 @@ extern "C" int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, 
         return HFRK_INVALID_CONFIG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t a_bytes = static_cast<size_t>(m) * k;
-    const size_t d_bytes = static_cast<size_t>(m) * n * 2;
+    const size_t d_bytes = static_cast<size_t>(m) * n * (d_dtype == HFRK_F32 ? 4 : 2);
     uint8_t* a_dev = static_cast<uint8_t*>(work_dev);
     uint8_t* d_dev = a_dev + (a_bytes + 255) / 256 * 256;
     HFRK_CUDA_TRY(cudaMemcpyAsync(a_dev, A_host, a_bytes, cudaMemcpyHostToDevice, s));

@@ -14,7 +14,7 @@ _LIB_NAME = "libhfrk_b200.so"
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 
 E4M3FN, E4M3FNUZ = 0, 1
-F16, BF16 = 0, 1
+F16, BF16, F32 = 0, 1, 2
 VARIANT_AUTO, VARIANT_CLUSTER, VARIANT_STREAMK = 0, 1, 2
 
 STATUS_NAMES = {
@@ -28,6 +28,8 @@ EXPORTED_SYMBOLS = (
     "hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
     "hfrk_host_call_workspace_bytes", "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan",
     "hfrk_device_status", "hfrk_last_error", "hfrk_version", "hfrk_skinny_gemm_fp8_profile",
+    "hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect", "hfrk_rowpar_connect_pointers",
+    "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
 )
 
 
@@ -50,6 +52,17 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_skinny_gemm_fp8_host.argtypes = common + [vp, vp]
     lib.hfrk_skinny_gemm_fp8_profile.argtypes = common + [i32, i32, i32, i32, i32, vp, vp]
     lib.hfrk_skinny_gemm_fp8_profile.restype = i32
+    lib.hfrk_rowpar_create.argtypes = [i32, i32, i32, i32, ctypes.POINTER(vp)]
+    lib.hfrk_rowpar_ipc_handle.argtypes = [vp, vp]
+    lib.hfrk_rowpar_connect.argtypes = [vp, vp]
+    lib.hfrk_rowpar_connect_pointers.argtypes = [vp, ctypes.POINTER(vp)]
+    lib.hfrk_rowpar_local_block.argtypes = [vp]
+    lib.hfrk_rowpar_local_block.restype = vp
+    lib.hfrk_rowpar_destroy.argtypes = [vp]
+    lib.hfrk_skinny_gemm_fp8_rowpar.argtypes = [vp] + common + [vp]
+    for name in ("hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect",
+                 "hfrk_rowpar_connect_pointers", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar"):
+        getattr(lib, name).restype = i32
     lib.hfrk_skinny_gemm_fp8_simt.argtypes = common + [vp]
     lib.hfrk_host_call_workspace_bytes.argtypes = [i32, i32, i32]
     lib.hfrk_host_call_workspace_bytes.restype = i64
@@ -90,7 +103,9 @@ def out_kind(dtype: torch.dtype) -> int:
         return F16
     if dtype == torch.bfloat16:
         return BF16
-    raise TypeError(f"expected float16 or bfloat16 output, got {dtype}")
+    if dtype == torch.float32:
+        return F32
+    raise TypeError(f"expected float16, bfloat16 or float32 output, got {dtype}")
 
 
 def _common_args(a: torch.Tensor, w: torch.Tensor, d: torch.Tensor, scale: torch.Tensor, accumulate: bool):

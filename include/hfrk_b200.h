@@ -50,7 +50,8 @@ enum hfrk_status {
  * multiplied by 0.5 per FNUZ operand on the device: for every bit pattern the reference's
  * quantiser can emit (hf_rocm_kernels/utils/fp8.py:17-29) value_fnuz == value_fn / 2 exactly. */
 enum hfrk_fp8_kind { HFRK_E4M3FN = 0, HFRK_E4M3FNUZ = 1 };
-enum hfrk_out_dtype { HFRK_F16 = 0, HFRK_BF16 = 1 };
+/* F32 output exists for unfused multi-GPU baselines (partial sums that a library all-reduce adds). */
+enum hfrk_out_dtype { HFRK_F16 = 0, HFRK_BF16 = 1, HFRK_F32 = 2 };
 
 /* The two kernels behind the GEMM.
  *   CLUSTER : one CTA per (128-row tile, K split); the K splits of a tile form a thread-block
@@ -109,6 +110,33 @@ int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, void* D_hos
                               int a_kind, int w_kind, int d_dtype, int accumulate,
                               void* work_dev, void* stream);
 int64_t hfrk_host_call_workspace_bytes(int m, int n, int k);
+
+/* ---- row-parallel (K split over GPUs) GEMM with the all-reduce fused into its epilogue ---------
+ * Rank r of `world` holds columns [r*K/world, (r+1)*K/world) of A and W. Every rank calls
+ * hfrk_skinny_gemm_fp8_rowpar with its shard; every rank ends with the full
+ *     D = D_in + scale * sum_r (A_r . W_r^T)
+ * (D_in must be the same on all ranks). Inside the kernel each CTA writes its fp32 partial tile
+ * into every peer's exchange buffer with plain stores over NVLink, publishes an epoch flag, waits
+ * (bounded, ~2 s: HFRK_DEVICE_TIMEOUT through hfrk_device_status) for the peers' flags and adds
+ * the contributions in rank order, so all ranks produce bit-identical results. One process per
+ * GPU: create -> exchange the 64-byte IPC handles by any host-side all-gather -> connect.
+ * The reference has no multi-GPU path at all (no collective call site exists in its tree); this
+ * stands where the benchmark specification asks for "GEMM + allreduce" in combined_ops.
+ * All ranks must issue the same sequence of calls on a group. A group serves one stream at a time.
+ *   max_m, max_n : largest call the group will see (sizes the exchange buffer:
+ *                  2 * world * min(max_m,16) * roundup(max_n,128) * 4 bytes + flags). */
+typedef struct hfrk_rowpar hfrk_rowpar;
+int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out);
+int hfrk_rowpar_ipc_handle(hfrk_rowpar* group, void* handle64_out);
+int hfrk_rowpar_connect(hfrk_rowpar* group, const void* all_handles /* world x 64 bytes, by rank */);
+/* Same-process alternative to the IPC route (all ranks' devices driven by one process with peer
+ * access enabled): the exchange blocks of all ranks, from hfrk_rowpar_local_block. */
+int hfrk_rowpar_connect_pointers(hfrk_rowpar* group, void* const* peer_blocks);
+void* hfrk_rowpar_local_block(hfrk_rowpar* group);
+int hfrk_rowpar_destroy(hfrk_rowpar* group);
+int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* group, const void* A_shard, const void* W_shard, void* D,
+                                const float* scale_dev, int m, int n, int k_shard, int64_t w_row_stride,
+                                int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);
 
 /* Plain SIMT (no TMA, no tensor core) kernel for the same operation. It exists to bisect faults
  * in the tensor-core path and as an on-device cross-check at sizes where a CPU check is slow.

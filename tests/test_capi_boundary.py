@@ -95,7 +95,7 @@ def test_argument_validation_happens_before_any_cuda_call(capi):
     assert call(a.data_ptr() + 1, *base[1:], 4, 128, 256, 256, 0, 0, 0, 1, 0, None) == 7  # alignment
     assert call(None, *base[1:], 4, 128, 256, 256, 0, 0, 0, 1, 0, None) == 6
     assert capi.lib.hfrk_skinny_gemm_fp8_simt(*base, 4, 128, 250, 256, 0, 0, 0, 1, None) == 3
-    assert capi.lib.hfrk_host_call_workspace_bytes(4, 128, 256) == 1024 + 1024
+    assert capi.lib.hfrk_host_call_workspace_bytes(4, 128, 256) == 1024 + 2048
     assert capi.lib.hfrk_host_call_workspace_bytes(0, 128, 256) == 0
 
 
