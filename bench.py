@@ -247,6 +247,9 @@ def run_ours(args):
     h2d = sum(c.m * c.k + (2 * c.m * c.n if c.bias else 0) for c in wl.cases(1))
     d2h = sum(2 * c.m * c.n for c in wl.cases(1))
 
+    # ---- multi-GPU extras: configuration 2 (N split, no collective) and 3 (K split, fused all-reduce)
+    multi = multi_gpu_extras(torch, dist, capi, wl, dev, rank, world) if world > 1 else None
+
     # ---- per-case times (rank 0 of a single-GPU run only; bounded)
     detail = None
     if world == 1 and not args.no_detail:
@@ -300,9 +303,81 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(torch, wl)
         if detail is not None:
             line["detail"] = detail
+        if multi is not None:
+            line["multi_gpu"] = multi
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _graph_time_us(torch, dist, dev, fns, reps=20, warm=5):
+    """Median microseconds per call of a graph of len(fns) calls, max over ranks."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        fns[0]()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for fn in fns:
+                fn()
+        times = []
+        for i in range(warm + reps):
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            e1.synchronize()
+            if i >= warm:
+                times.append(e0.elapsed_time(e1) * 1000.0 / len(fns))
+    t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def multi_gpu_extras(torch, dist, capi, wl, dev, rank, world):
+    """Strong-scaling figures of the two sharding modes at M=16 (and M=1), all ranks in step."""
+    from hf_rocm_kernels.combined_ops import RowParallelSkinnyGemm, skinny_gemm_then_allreduce
+
+    out = {"world": world, "config2_n_split": [], "config3_k_split_fused_allreduce": []}
+    scale = torch.full((1,), 1e-4, device=dev)
+
+    def rand_fp8(rows, cols):
+        return torch.randint(0, 120, (rows, cols), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+
+    # configuration 2: each rank holds N/world rows of the 70B projections; no collective
+    for name, (n, k) in wl.LLAMA3_70B.items():
+        rows = n // world
+        copies = max(8, -(-2 * L2_BYTES // (rows * k)))
+        ws = [rand_fp8(rows, k) for _ in range(copies)]
+        for m in (1, 16):
+            a = rand_fp8(m, k)
+            d = torch.zeros((m, rows), dtype=torch.bfloat16, device=dev)
+            us = _graph_time_us(torch, dist, dev, [lambda w=w: capi.check(capi.skinny_gemm(a, w, d, scale)) for w in ws])
+            out["config2_n_split"].append({"case": f"70b_{name}_m{m}", "rows_per_gpu": rows, "us_per_call": round(us, 2),
+                                           "aggregate_weight_tbps": round(n * k / us / 1e6, 3)})
+        del ws
+    # configuration 3: K split of the 70B down projection, all-reduce fused into the epilogue
+    n, k = 8192, 28672
+    k_shard = k // world
+    group = RowParallelSkinnyGemm(max_m=16, max_n=n)
+    copies = max(8, -(-2 * L2_BYTES // (n * k_shard)))
+    ws = [rand_fp8(n, k_shard) for _ in range(copies)]
+    for m in (1, 2, 8, 16):
+        a = rand_fp8(m, k_shard)
+        d = torch.zeros((m, n), dtype=torch.bfloat16, device=dev)
+        partial = torch.empty((m, n), dtype=torch.float32, device=dev)
+        fused = _graph_time_us(torch, dist, dev, [lambda w=w: group(a, w, scale, d) for w in ws])
+        unfused = _graph_time_us(torch, dist, dev,
+                                 [lambda w=w: skinny_gemm_then_allreduce(a, w, scale, d, partial) for w in ws])
+        local = _graph_time_us(torch, dist, dev, [lambda w=w: capi.check(capi.skinny_gemm(a, w, d, scale)) for w in ws])
+        out["config3_k_split_fused_allreduce"].append({
+            "m": m, "k_per_gpu": k_shard, "us_fused": round(fused, 2), "us_gemm_plus_nccl_allreduce": round(unfused, 2),
+            "us_local_gemm_only": round(local, 2), "nvlink_bytes_out_per_gpu": (world - 1) * 4 * m * n})
+    torch.cuda.synchronize()
+    dist.barrier()
+    group.close()
+    return out
 
 
 def cpu_sample(torch, wl):

@@ -147,7 +147,8 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
             if (slot[i] != 0xffffffffu) dst[slot[i]] = val[i];
         }
     }
-    __threadfence_system();
+    // The CTA barrier orders every thread's stores before the flag writers; their system-scope
+    // release is cumulative over them, so one fence per peer replaces one per thread.
     asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
     bool ok = true;
     const int t = static_cast<int>(threadIdx.x);
@@ -605,16 +606,16 @@ struct Plan {
 int round_up(int v, int to) { return (v + to - 1) / to * to; }
 
 // Launch shape of the cluster kernel for one launch of m <= kMaxMPad tokens, from sweeps on B200
-// (148 SMs) over the Llama-3 8B/70B projection shapes:
-//   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream, and several
-//     small CTAs per SM hide each other's fill, drain and reduction better than one big one:
-//     with a K split the ring is sized so that THREE CTAs fit an SM (3 stages of 18 KiB at
-//     16 tokens, 4 at a single token, whose receive buffer is tiny);
-//   * the whole grid must be resident at once. A cluster that has to wait for a free slot starts
-//     late and then streams alone at a fraction of the bandwidth, which costs far more than a
-//     slightly uneven spread: the split is the largest one (up to 8, or 16 for very narrow
-//     matrices) that keeps tiles * split within 3 * 148 CTAs, with at least two K blocks each;
-//   * without a split (tiles alone cover the SMs) a deeper ring and two CTAs per SM are best.
+// (148 SMs) over the Llama-3 8B/70B projection shapes and their 2/4/8-way N and K shards:
+//   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream, and two small
+//     CTAs per SM hide each other's fill, drain and reduction better than one big one: with a K
+//     split the ring has four 18 KiB stages (two CTAs per SM at 16 tokens);
+//   * the whole grid must be resident at once, WITH MARGIN. A cluster that has to wait for a free
+//     slot starts late and then streams alone at a fraction of the bandwidth, and clusters only
+//     fit into one GPC, so a grid that fills the last slot on paper (288 of 296) already spills.
+//     The split is the largest one with tiles * split <= 280 and at least two K blocks per CTA,
+//     capped at 8 (12 below 25 tiles, 16 below 11: very narrow shards need it to reach the SMs);
+//   * without a split (tiles alone cover the SMs) a ring of six stages, two CTAs per SM.
 int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
     if (split_req < 0 || split_req > kMaxSplit || stages_req < 0 || stages_req == 1 || stages_req > kMaxStages)
@@ -623,14 +624,14 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     const int tiles = (n + kTileN - 1) / kTileN;
     const int nkb = (k + kBlockK - 1) / kBlockK;
     const int stage_bytes = kWStageBytes + m_pad * kBlockK;
-    constexpr int kCtasPerSmSplit = 3;
-    constexpr int kResident = kCtasPerSmSplit * kNumSms;
+    constexpr int kResidentTarget = 280;
 
     int split = split_req;
     if (split == 0) {
-        split = kResident / tiles;
-        const int cap = tiles * 8 < kNumSms ? kMaxSplit : 8;
+        split = kResidentTarget / tiles;
+        const int cap = tiles <= 10 ? kMaxSplit : (tiles <= 24 ? 12 : 8);
         if (split > cap) split = cap;
+        if (split < 2 && tiles < kNumSms) split = 2;  // 141..147 tiles: two CTAs per SM still beat one
         if (split > nkb / 2) split = nkb / 2;
         if (split < 1) split = 1;
     }
@@ -640,15 +641,10 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     const int recv_bytes = split > 1 ? split * chunk * 4 : 0;
     const int fixed_bytes = 1024 + kCtrlBytes + recv_bytes;
     const int max_stages_fit = (kSmemLimit - fixed_bytes) / stage_bytes;
-    int stages = stages_req;
-    if (stages == 0) {
-        if (split > 1) {
-            const int per_cta = 228 * 1024 / kCtasPerSmSplit - 1024;
-            stages = (per_cta - fixed_bytes) / stage_bytes;
-            if (stages < 2) stages = 2;
-        } else {
-            stages = 6;
-        }
+    int stages = stages_req != 0 ? stages_req : (split > 1 ? 4 : 6);
+    if (stages_req == 0 && split > 1) {
+        // keep two CTAs on an SM when the receive buffer of a larger token count grows
+        while (stages > 2 && 2 * (fixed_bytes + stages * stage_bytes + 1024) > 228 * 1024) --stages;
     }
     if (stages > max_stages_fit) stages = max_stages_fit;
     if (stages > kMaxStages) stages = kMaxStages;

@@ -44,12 +44,12 @@ def test_version(capi):
 
 
 def test_plan_covers_the_sms(capi):
-    # fewer tiles than SMs -> the largest K split whose grid is resident at once, three CTAs per SM
+    # fewer tiles than SMs -> the largest K split whose grid is resident at once (with margin), two CTAs per SM
     for (m, n, k) in [(16, 4096, 4096), (16, 6144, 4096), (16, 4096, 14336), (16, 8192, 8192), (1, 8192, 28672)]:
         p = capi.plan(m, n, k)
         assert p["variant"] == capi.VARIANT_CLUSTER and p["tiles"] == (n + 127) // 128
-        assert 148 <= p["ctas"] <= 3 * 148 and p["ctas"] == p["tiles"] * p["split_k"]
-        assert p["k_blocks"] // p["split_k"] >= 2 and 3 * (p["smem_bytes"] + 1024) <= 228 * 1024
+        assert 148 <= p["ctas"] <= 280 and p["ctas"] == p["tiles"] * p["split_k"]
+        assert p["k_blocks"] // p["split_k"] >= 2 and 2 * (p["smem_bytes"] + 1024) <= 228 * 1024
     # enough tiles -> no split, deeper ring
     for (m, n, k) in [(16, 28672, 4096), (4, 57344, 8192)]:
         p = capi.plan(m, n, k)
