@@ -946,8 +946,148 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
     return HFRK_SUCCESS;
 }
 
+
 }  // namespace
 }  // namespace hfrk
+
+// =============================================================================== no-allocation entry
+namespace hfrk {
+namespace {
+
+// Some callers must not allocate device memory at the moment they call a GEMM: a serving engine
+// that has handed the whole of HBM to its own pools at start-up (a later cudaMalloc would fail or
+// fragment them), code that runs between two allocator check-points, a plug-in that is forbidden
+// to touch the allocator of its host. For them the stream-K kernel is offered with its scratch in
+// a fixed array that is part of the library image: nothing is allocated, ever. The price is that
+// every GPU that loads the library carries the array until the process ends, that the sizes are
+// capped, and that all calls share the one array.
+//   partials : 2 slots per CTA x 296 CTAs x 16 tokens x 128 rows x 4 B  = 4,849,664 B
+//   counters : one per 128-row tile, 4096 tiles (N <= 524,288)           =    16,384 B
+constexpr int kStaticMaxTokens = 16;
+constexpr int kStaticMaxTiles = 4096;
+constexpr size_t kStaticPartialBytes = static_cast<size_t>(2) * kSkMaxGrid * kStaticMaxTokens * kTileN * sizeof(float);
+constexpr size_t kStaticCounterBytes = static_cast<size_t>(kStaticMaxTiles) * sizeof(unsigned int);
+}  // namespace
+}  // namespace hfrk
+
+static __device__ __align__(256) unsigned char g_static_scratch[hfrk::kStaticPartialBytes + hfrk::kStaticCounterBytes];
+
+namespace hfrk {
+namespace {
+
+// In host code the array's name is only a handle for the runtime, not a device address; the
+// address the kernel needs is asked for once per device, with that device current.
+int static_scratch_address(unsigned char** out) {
+    static std::mutex mu;
+    static unsigned char* address[64] = {};
+    int dev = 0;
+    HFRK_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return HFRK_INVALID_CONFIG;
+    std::lock_guard<std::mutex> lock(mu);
+    if (address[dev] == nullptr) {
+        void* ptr = nullptr;
+        HFRK_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (ptr == nullptr) {
+            set_last_error("cudaGetSymbolAddress returned no address for the static scratch array");
+            return HFRK_CUDA_ERROR;
+        }
+        address[dev] = static_cast<unsigned char*>(ptr);
+    }
+    *out = address[dev];
+    return HFRK_SUCCESS;
+}
+
+// Tensor map without the host-side cache (the cache grows a heap-allocated table).
+int encode_tensor_map_uncached(const void* base, uint64_t inner, uint64_t outer, uint64_t stride, uint32_t box_outer,
+                               CUtensorMap* out) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+        return HFRK_CUDA_ERROR;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {stride};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_outer};
+    cuuint32_t elem_strides[2] = {1, 1};
+    CUresult res = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed for the no-allocation entry point");
+        return HFRK_CUDA_ERROR;
+    }
+    return HFRK_SUCCESS;
+}
+
+}  // namespace
+}  // namespace hfrk
+
+extern "C" int hfrk_skinny_gemm_fp8_noalloc(const void* A, const void* W, void* D, const float* scale_dev, int m,
+                                            int n, int k, int64_t w_row_stride, int a_kind, int w_kind, int d_dtype,
+                                            int accumulate, void* stream) {
+    using namespace hfrk;
+    int rc = validate(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype);
+    if (rc != HFRK_SUCCESS) return rc;
+    const int tiles = (n + kTileN - 1) / kTileN;
+    if (m > kStaticMaxTokens || tiles > kStaticMaxTiles) {
+        set_last_error("hfrk_skinny_gemm_fp8_noalloc: at most 16 tokens and N <= 524288 (fixed scratch array)");
+        return HFRK_TOO_LARGE;
+    }
+    rc = prepare_device_once();
+    if (rc != HFRK_SUCCESS) return rc;
+    unsigned char* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc != HFRK_SUCCESS) return rc;
+    SkPlan plan;
+    rc = make_sk_plan(m, n, k, /*ctas_per_sm=*/2, /*stages_req=*/0, &plan);
+    if (rc != HFRK_SUCCESS) return rc;
+    if (plan.grid > kSkMaxGrid) return HFRK_TOO_LARGE;
+
+    CUtensorMap tmap_w, tmap_a;
+    rc = encode_tensor_map_uncached(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                                    static_cast<uint64_t>(w_row_stride), kTileN, &tmap_w);
+    if (rc != HFRK_SUCCESS) return rc;
+    rc = encode_tensor_map_uncached(A, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                                    static_cast<uint32_t>(plan.m_pad), &tmap_a);
+    if (rc != HFRK_SUCCESS) return rc;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(scratch + kStaticPartialBytes);
+    // The array keeps whatever the last call left. Partials are fully rewritten before they are
+    // read; the tile counters must start at zero, so the ones this call uses are cleared here.
+    HFRK_CUDA_TRY(cudaMemsetAsync(counters, 0, static_cast<size_t>(tiles) * sizeof(unsigned int), s));
+
+    SkParams p;
+    p.d = D;
+    p.scale = scale_dev;
+    p.kind_factor = (a_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f) * (w_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f);
+    p.m = m;
+    p.n = n;
+    p.m_pad = plan.m_pad;
+    p.nkb = plan.nkb;
+    p.total_units = plan.tiles * plan.nkb;
+    p.stages = plan.stages;
+    p.d_dtype = d_dtype;
+    p.accumulate = accumulate ? 1 : 0;
+    p.partials = reinterpret_cast<float*>(scratch);
+    p.counters = counters;
+    p.stamps = nullptr;
+
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(plan.grid), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+    cfg.stream = s;
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+    if (plan.units_per_stage == 1) {
+        HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_streamk_kernel<1>, tmap_w, tmap_a, p));
+    } else {
+        HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_streamk_kernel<2>, tmap_w, tmap_a, p));
+    }
+    return HFRK_SUCCESS;
+}
 
 
 // =============================================================================== row-parallel group

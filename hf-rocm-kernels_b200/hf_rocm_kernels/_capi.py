@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_device_status", "hfrk_last_error", "hfrk_version", "hfrk_skinny_gemm_fp8_profile",
     "hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect", "hfrk_rowpar_connect_pointers",
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
+    "hfrk_skinny_gemm_fp8_noalloc",
 )
 
 
@@ -64,6 +65,8 @@ def _load() -> ctypes.CDLL:
                  "hfrk_rowpar_connect_pointers", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar"):
         getattr(lib, name).restype = i32
     lib.hfrk_skinny_gemm_fp8_simt.argtypes = common + [vp]
+    lib.hfrk_skinny_gemm_fp8_noalloc.argtypes = common + [vp]
+    lib.hfrk_skinny_gemm_fp8_noalloc.restype = i32
     lib.hfrk_host_call_workspace_bytes.argtypes = [i32, i32, i32]
     lib.hfrk_host_call_workspace_bytes.restype = i64
     lib.hfrk_skinny_gemm_plan.argtypes = [i32, i32, i32, i32, i32, i32, ctypes.POINTER(i32)]
@@ -149,6 +152,14 @@ def skinny_gemm_simt(a, w, d, scale, accumulate=True, stream=None) -> int:
     with torch.cuda.device(a.device):
         return lib.hfrk_skinny_gemm_fp8_simt(*_common_args(a, w, d, scale, accumulate),
                                              _stream_ptr(stream, a.device))
+
+
+def skinny_gemm_noalloc(a, w, d, scale, accumulate=True, stream=None) -> int:
+    """``hfrk_skinny_gemm_fp8_noalloc``: the GEMM with its scratch in a fixed array of the library
+    image, for callers that may not allocate device memory (m <= 16, n <= 524288)."""
+    with torch.cuda.device(a.device):
+        return lib.hfrk_skinny_gemm_fp8_noalloc(*_common_args(a, w, d, scale, accumulate),
+                                                _stream_ptr(stream, a.device))
 
 
 def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True, stream=None) -> int:

@@ -138,6 +138,23 @@ int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* group, const void* A_shard, const v
                                 const float* scale_dev, int m, int n, int k_shard, int64_t w_row_stride,
                                 int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);
 
+/* The GEMM for callers that must not allocate device memory when they call it: an inference
+ * server whose own pools already own all of HBM (a late cudaMalloc fails or fragments them), code
+ * that runs between allocator check-points, a plug-in barred from its host's allocator. It runs
+ * the stream-K kernel with its scratch (fp32 partial tiles + tile counters) in a fixed array
+ * inside the library image -- 4,866,048 bytes that every GPU loading the library holds until the
+ * process exits -- and calls no cudaMalloc, cudaFree or any allocating routine, on any call.
+ * Limits: m <= 16 and n <= 524,288, otherwise HFRK_TOO_LARGE (hfrk_last_error says why); the
+ * caller still passes A, W, D and the scale. The first call on a device looks up the array's
+ * device address (cudaGetSymbolAddress, with that device current), so make that first call
+ * before any stream capture. All calls share the one array, which keeps what the last call left:
+ * the tile counters a call uses are cleared on `stream` before its kernel, partials are always
+ * written before they are read; two calls that overlap on the GPU (different streams) race on it.
+ * Plain launch (no programmatic dependent launch). It has no counterpart in the reference. */
+int hfrk_skinny_gemm_fp8_noalloc(const void* A, const void* W, void* D, const float* scale_dev,
+                                 int m, int n, int k, int64_t w_row_stride,
+                                 int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);
+
 /* Plain SIMT (no TMA, no tensor core) kernel for the same operation. It exists to bisect faults
  * in the tensor-core path and as an on-device cross-check at sizes where a CPU check is slow.
  * It is never selected by hfrk_skinny_gemm_fp8. No counterpart in the reference. */
