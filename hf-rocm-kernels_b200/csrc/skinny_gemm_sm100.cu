@@ -55,15 +55,15 @@ static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
 
 // Row-parallel (K split over GPUs) exchange state, as seen by the kernel of ONE rank. Every rank
 // owns an exchange buffer that its peers write into over NVLink:
-//   data  : float [2 parities][world sources][elems_per_src]   partial sums, fp32
-//   flags : u32   [2 parities][world sources][flags_per_src]   epoch numbers, one per (tile, K-split rank)
-// data[p] / flags[p] are the bases of rank p's buffer (p == rank: the local one).
+//   cells : {fp32 partial sum, epoch} [2 parities][world sources][elems_per_src], 8 bytes each
+// A cell is written with ONE 8-byte store, so its reader sees value and epoch together: a cell
+// whose epoch equals the current call's is valid. No flag, no fence and no barrier is needed
+// between writer and reader. cells[p] is the base of rank p's buffer (p == rank: the local one).
 constexpr int kMaxWorld = 8;
 struct RowparDev {
     int rank, world;
-    unsigned int elems_per_src, flags_per_src;
-    float* data[kMaxWorld];
-    unsigned int* flags[kMaxWorld];
+    unsigned int elems_per_src;
+    uint2* cells[kMaxWorld];
     unsigned int* call_index;   // local: number of completed calls on this communicator
     unsigned int* done_ctas;    // local: CTAs of the running call that have finished
 };
@@ -95,68 +95,67 @@ __device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
 
 
 // ---------------------------------------------------------------- cross-GPU exchange (row-parallel)
-__device__ __forceinline__ void st_release_sys(unsigned int* ptr, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys_v2(uint2* ptr, uint32_t x, uint32_t y) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(x), "r"(y) : "memory");
 }
 
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* ptr) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* ptr) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
     return v;
 }
 
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* ptr) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
-    return v;
-}
-
-// AND of a predicate over the 128 epilogue threads (named barrier 1 with reduction).
-__device__ __forceinline__ bool epilogue_vote_all(bool pred) {
-    uint32_t out;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred pin, pout;\n\t"
-        "setp.ne.u32 pin, %1, 0;\n\t"
-        "barrier.cta.red.and.pred pout, 1, %2, pin;\n\t"
-        "selp.u32 %0, 1, 0, pout;\n\t"
-        "}\n"
-        : "=r"(out)
-        : "r"(pred ? 1u : 0u), "r"(kEpilogueThreads)
-        : "memory");
-    return out != 0;
-}
-
-// One-shot all-reduce of the values the 128 epilogue threads of this CTA own, fused into the GEMM
-// epilogue. Each thread holds CNT partial sums (`val`), `slot[i]` is the element's index in the
-// exchange buffer (0xffffffff = unused). The CTA writes its partials into every peer's buffer
-// (plain stores to peer memory: NVLink), publishes one epoch-valued flag per peer, waits (bounded)
-// for the matching flag of every peer, and adds the `world` contributions in rank order, so that
-// all ranks compute bit-identical sums. Returns false if a peer did not show up in time.
+// One-shot all-reduce of the values this thread owns, fused into the GEMM epilogue. `val` holds
+// CNT partial sums, `slot[i]` the element's index in the exchange buffer (0xffffffff = unused).
+// The thread writes {value, epoch} cells into every peer's buffer (plain 8-byte stores to peer
+// memory: NVLink), then polls the matching cells of its own buffer until each carries this call's
+// epoch (bounded), and adds the `world` contributions in rank order, so that all ranks compute
+// bit-identical sums. Nothing here synchronises the CTA. Returns false if a peer did not deliver
+// in time (the status word is set).
 template <int CNT>
-__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, unsigned int flag_slot,
-                                                const uint32_t (&slot)[CNT], float (&val)[CNT],
-                                                volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
+                                                float (&val)[CNT], volatile uint32_t* abort_flag) {
     const unsigned int parity = epoch & 1u;
     const size_t my_src = static_cast<size_t>(parity * rp.world + rp.rank);
     for (int peer = 0; peer < rp.world; ++peer) {
         if (peer == rp.rank) continue;
-        float* dst = rp.data[peer] + my_src * rp.elems_per_src;
+        uint2* dst = rp.cells[peer] + my_src * rp.elems_per_src;
 #pragma unroll
         for (int i = 0; i < CNT; ++i) {
-            if (slot[i] != 0xffffffffu) dst[slot[i]] = val[i];
+            if (slot[i] != 0xffffffffu) st_relaxed_sys_v2(dst + slot[i], __float_as_uint(val[i]), epoch);
         }
     }
-    // The CTA barrier orders every thread's stores before the flag writers; their system-scope
-    // release is cumulative over them, so one fence per peer replaces one per thread.
-    asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+    // Cells are fetched a batch at a time (4 elements x up to 7 peers in flight per thread) and the
+    // batch is re-read until every cell shows the epoch; batches of unused elements are skipped,
+    // which is the common case: a thread usually owns two or three elements of the tile.
+    constexpr int kBatch = 4;
     bool ok = true;
-    const int t = static_cast<int>(threadIdx.x);
-    if (t < rp.world && t != rp.rank) {
-        st_release_sys(rp.flags[t] + my_src * rp.flags_per_src + flag_slot, epoch);
-        const unsigned int* mine = rp.flags[rp.rank] + static_cast<size_t>(parity * rp.world + t) * rp.flags_per_src + flag_slot;
-        const long long start = clock64();
-        while (ld_acquire_sys(mine) != epoch) {
+    const long long start = clock64();
+#pragma unroll
+    for (int i0 = 0; i0 < CNT; i0 += kBatch) {
+        bool any = false;
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) any |= slot[i0 + b] != 0xffffffffu;
+        if (!any || !ok) continue;
+        uint32_t got[kBatch][kMaxWorld];
+        for (;;) {
+            bool ready = true;
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+#pragma unroll
+                for (int src = 0; src < kMaxWorld; ++src) {
+                    got[b][src] = 0u;
+                    if (src < rp.world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
+                        const uint2 cell = ld_relaxed_sys_v2(rp.cells[rp.rank] +
+                                                             static_cast<size_t>(parity * rp.world + src) *
+                                                                 rp.elems_per_src +
+                                                             slot[i0 + b]);
+                        got[b][src] = cell.x;
+                        ready &= cell.y == epoch;
+                    }
+                }
+            }
+            if (ready) break;
             if (*abort_flag || clock64() - start > kWaitLimitCycles) {
                 *abort_flag = 1u;
                 record_timeout(kRolePeer);
@@ -164,48 +163,23 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
                 break;
             }
         }
-    }
-    ok = epilogue_vote_all(ok);
-    if (!ok) return false;
-    // Loads are issued a batch at a time (4 elements x up to 7 peers in flight per thread); batches
-    // whose elements are all unused are skipped, which is the common case: a thread usually owns
-    // two or three elements of the tile.
-    constexpr int kBatch = 4;
-#pragma unroll
-    for (int i0 = 0; i0 < CNT; i0 += kBatch) {
-        bool any = false;
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) any |= slot[i0 + b] != 0xffffffffu;
-        if (!any) continue;
-        float got[kBatch][kMaxWorld];
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-#pragma unroll
-            for (int src = 0; src < kMaxWorld; ++src) {
-                got[b][src] = 0.0f;
-                if (src < rp.world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
-                    got[b][src] = ld_relaxed_sys_f32(rp.data[rp.rank] +
-                                                     static_cast<size_t>(parity * rp.world + src) * rp.elems_per_src +
-                                                     slot[i0 + b]);
-                }
-            }
-        }
+        if (!ok) continue;
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
             float sum = 0.0f;
 #pragma unroll
             for (int src = 0; src < kMaxWorld; ++src) {
-                if (src < rp.world) sum += (src == rp.rank) ? val[i0 + b] : got[b][src];
+                if (src < rp.world) sum += (src == rp.rank) ? val[i0 + b] : __uint_as_float(got[b][src]);
             }
             val[i0 + b] = sum;
         }
     }
-    return true;
+    return ok;
 }
 
 // kRowPar: the epilogue all-reduces the tile over the ranks of a row-parallel group before D is written.
 template <bool kRowPar>
-__global__ void __launch_bounds__(kThreads, kRowPar ? 3 : 1)
+__global__ void __launch_bounds__(kThreads, kRowPar ? 2 : 1)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -391,7 +365,6 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         bool ok = mbar_wait_bounded(accum_bar, 0u, &ctrl->abort, kRoleEpilogue);
         ok = __all_sync(0xffffffffu, ok) && ctrl->abort == 0u;
         ok = __all_sync(0xffffffffu, ok);
-        if (kRowPar) ok = epilogue_vote_all(ok);  // the exchange below contains CTA-wide barriers
         if (threadIdx.x == 0) stamp(p, 5);
         tcgen05_fence_after_sync();
         float* const partial = reinterpret_cast<float*>(ring_ptr);  // the ring is idle by now
@@ -410,7 +383,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                             val[j] = __uint_as_float(v[j]);
                             slot[j] = j < p.m ? tile_slot0 + static_cast<uint32_t>(j * kTileN + nl) : 0xffffffffu;
                         }
-                        if (!rowpar_exchange<16>(p.rp, epoch, blockIdx.x * kMaxSplit, slot, val, &ctrl->abort)) ok = false;
+                        if (!rowpar_exchange<16>(p.rp, epoch, slot, val, &ctrl->abort)) ok = false;
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(val[j]);
                     }
@@ -446,7 +419,6 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
             bool landed = ok && mbar_wait_bounded(recv_bar, 0u, &ctrl->abort, kRoleEpilogue);
             landed = __all_sync(0xffffffffu, landed);
-            if (kRowPar) landed = epilogue_vote_all(landed);
             if (landed) {
                 const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
                 float own[kOwned];
@@ -463,7 +435,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     slot[it] = (off < chunk && e < total) ? tile_slot0 + static_cast<uint32_t>(e) : 0xffffffffu;
                 }
                 if (kRowPar) {
-                    landed = rowpar_exchange<kOwned>(p.rp, epoch, blockIdx.x * kMaxSplit + rank, slot, own, &ctrl->abort);
+                    landed = rowpar_exchange<kOwned>(p.rp, epoch, slot, own, &ctrl->abort);
                 }
 #pragma unroll
                 for (int it = 0; it < kOwned; ++it) {
@@ -910,9 +882,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         if (rowpar != nullptr) {
             p.rp = *rowpar;
             const unsigned tiles = static_cast<unsigned>((n + kTileN - 1) / kTileN);
-            if (static_cast<unsigned long long>(tiles) * mc * kTileN > p.rp.elems_per_src ||
-                tiles * kMaxSplit > p.rp.flags_per_src)
-                return HFRK_TOO_LARGE;
+            if (static_cast<unsigned long long>(tiles) * mc * kTileN > p.rp.elems_per_src) return HFRK_TOO_LARGE;
         }
 
         cudaLaunchConfig_t cfg;
@@ -1095,25 +1065,10 @@ struct hfrk_rowpar {
     hfrk::RowparDev dev;
     uint8_t* local_block = nullptr;
     size_t block_bytes = 0;
-    size_t flags_offset = 0;
     void* opened[hfrk::kMaxWorld] = {};   // peer mappings opened from IPC handles
     int device = 0;
     bool connected = false;
 };
-
-namespace hfrk {
-namespace {
-
-size_t rowpar_data_bytes(int world, unsigned elems_per_src) { return static_cast<size_t>(2) * world * elems_per_src * 4; }
-size_t rowpar_flag_bytes(int world, unsigned flags_per_src) { return static_cast<size_t>(2) * world * flags_per_src * 4; }
-
-void rowpar_point(hfrk_rowpar* g, int peer, uint8_t* base) {
-    g->dev.data[peer] = reinterpret_cast<float*>(base);
-    g->dev.flags[peer] = reinterpret_cast<unsigned int*>(base + g->flags_offset);
-}
-
-}  // namespace
-}  // namespace hfrk
 
 extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out) {
     if (out == nullptr || world < 1 || world > hfrk::kMaxWorld || rank < 0 || rank >= world || max_m < 1 ||
@@ -1125,11 +1080,8 @@ extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfr
     g->dev.rank = rank;
     g->dev.world = world;
     g->dev.elems_per_src = static_cast<unsigned>(tiles) * m_cap * hfrk::kTileN;
-    g->dev.flags_per_src = static_cast<unsigned>(tiles) * hfrk::kMaxSplit;
-    const size_t data = (hfrk::rowpar_data_bytes(world, g->dev.elems_per_src) + 255) / 256 * 256;
-    const size_t flags = (hfrk::rowpar_flag_bytes(world, g->dev.flags_per_src) + 255) / 256 * 256;
-    g->flags_offset = data;
-    g->block_bytes = data + flags + 256;
+    const size_t cells = (static_cast<size_t>(2) * world * g->dev.elems_per_src * sizeof(uint2) + 255) / 256 * 256;
+    g->block_bytes = cells + 256;
     cudaError_t err = cudaGetDevice(&g->device);
     if (err == cudaSuccess) err = cudaMalloc(&g->local_block, g->block_bytes);
     if (err == cudaSuccess) err = cudaMemset(g->local_block, 0, g->block_bytes);
@@ -1139,8 +1091,8 @@ extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfr
         delete g;
         return HFRK_CUDA_ERROR;
     }
-    hfrk::rowpar_point(g, rank, g->local_block);
-    g->dev.call_index = reinterpret_cast<unsigned int*>(g->local_block + data + flags);
+    g->dev.cells[rank] = reinterpret_cast<uint2*>(g->local_block);
+    g->dev.call_index = reinterpret_cast<unsigned int*>(g->local_block + cells);
     g->dev.done_ctas = g->dev.call_index + 1;
     g->connected = world == 1;
     *out = g;
@@ -1165,7 +1117,7 @@ extern "C" int hfrk_rowpar_connect(hfrk_rowpar* g, const void* all_handles) {
         void* mapped = nullptr;
         HFRK_CUDA_TRY(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
         g->opened[peer] = mapped;
-        hfrk::rowpar_point(g, peer, static_cast<uint8_t*>(mapped));
+        g->dev.cells[peer] = static_cast<uint2*>(mapped);
     }
     g->connected = true;
     return HFRK_SUCCESS;
@@ -1176,7 +1128,7 @@ extern "C" int hfrk_rowpar_connect_pointers(hfrk_rowpar* g, void* const* peer_bl
     for (int peer = 0; peer < g->dev.world; ++peer) {
         if (peer == g->dev.rank) continue;
         if (peer_blocks[peer] == nullptr) return HFRK_BAD_WORLD;
-        hfrk::rowpar_point(g, peer, static_cast<uint8_t*>(peer_blocks[peer]));
+        g->dev.cells[peer] = static_cast<uint2*>(peer_blocks[peer]);
     }
     g->connected = true;
     return HFRK_SUCCESS;

@@ -115,16 +115,18 @@ int64_t hfrk_host_call_workspace_bytes(int m, int n, int k);
  * Rank r of `world` holds columns [r*K/world, (r+1)*K/world) of A and W. Every rank calls
  * hfrk_skinny_gemm_fp8_rowpar with its shard; every rank ends with the full
  *     D = D_in + scale * sum_r (A_r . W_r^T)
- * (D_in must be the same on all ranks). Inside the kernel each CTA writes its fp32 partial tile
- * into every peer's exchange buffer with plain stores over NVLink, publishes an epoch flag, waits
- * (bounded, ~2 s: HFRK_DEVICE_TIMEOUT through hfrk_device_status) for the peers' flags and adds
- * the contributions in rank order, so all ranks produce bit-identical results. One process per
+ * (D_in must be the same on all ranks). Inside the kernel each thread writes the partial sums it
+ * owns into every peer's exchange buffer as 8-byte {value, call number} cells (plain stores over
+ * NVLink; a cell is valid once it carries the current call number, so no flag or fence is
+ * needed), polls its own buffer for the peers' cells (bounded, ~2 s: HFRK_DEVICE_TIMEOUT through
+ * hfrk_device_status) and adds the contributions in rank order, so all ranks produce
+ * bit-identical results. One process per
  * GPU: create -> exchange the 64-byte IPC handles by any host-side all-gather -> connect.
  * The reference has no multi-GPU path at all (no collective call site exists in its tree); this
  * stands where the benchmark specification asks for "GEMM + allreduce" in combined_ops.
  * All ranks must issue the same sequence of calls on a group. A group serves one stream at a time.
  *   max_m, max_n : largest call the group will see (sizes the exchange buffer:
- *                  2 * world * min(max_m,16) * roundup(max_n,128) * 4 bytes + flags). */
+ *                  2 * world * min(max_m,16) * roundup(max_n,128) * 8 bytes). */
 typedef struct hfrk_rowpar hfrk_rowpar;
 int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out);
 int hfrk_rowpar_ipc_handle(hfrk_rowpar* group, void* handle64_out);
