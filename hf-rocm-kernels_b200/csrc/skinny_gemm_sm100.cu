@@ -1234,6 +1234,29 @@ extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split
     return HFRK_SUCCESS;
 }
 
+extern "C" int hfrk_max_active_clusters(int split, int smem_bytes, int* clusters_out) {
+    if (clusters_out == nullptr || split < 1 || split > hfrk::kMaxSplit || smem_bytes < 0 || smem_bytes > hfrk::kSmemLimit)
+        return HFRK_INVALID_CONFIG;
+    int rc = hfrk::prepare_device_once();
+    if (rc != HFRK_SUCCESS) return rc;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(1, static_cast<unsigned>(split), 1);
+    cfg.blockDim = dim3(hfrk::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = static_cast<unsigned>(split);
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    HFRK_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, hfrk::skinny_gemm_fp8_sm100_kernel<false>, &cfg));
+    *clusters_out = clusters;
+    return HFRK_SUCCESS;
+}
+
 extern "C" int hfrk_device_status(int clear, unsigned int* word_out) {
     unsigned int word = 0;
     HFRK_CUDA_TRY(cudaMemcpyFromSymbol(&word, hfrk::g_device_status, sizeof(word)));

@@ -30,7 +30,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_device_status", "hfrk_last_error", "hfrk_version", "hfrk_skinny_gemm_fp8_profile",
     "hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect", "hfrk_rowpar_connect_pointers",
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
-    "hfrk_skinny_gemm_fp8_noalloc",
+    "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters",
 )
 
 
@@ -71,6 +71,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_host_call_workspace_bytes.restype = i64
     lib.hfrk_skinny_gemm_plan.argtypes = [i32, i32, i32, i32, i32, i32, ctypes.POINTER(i32)]
     lib.hfrk_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_uint)]
+    lib.hfrk_max_active_clusters.argtypes = [i32, i32, ctypes.POINTER(i32)]
+    lib.hfrk_max_active_clusters.restype = i32
     lib.hfrk_last_error.restype = ctypes.c_char_p
     for name in ("hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
                  "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan", "hfrk_device_status", "hfrk_version"):
@@ -180,6 +182,12 @@ def plan(m: int, n: int, k: int, variant: int = VARIANT_AUTO, split_k: int = 0, 
     check(lib.hfrk_skinny_gemm_plan(m, n, k, variant, split_k, ctas_per_sm, out))
     keys = ("variant", "split_k", "num_stages", "ctas", "smem_bytes", "m_pad", "k_blocks", "tiles")
     return dict(zip(keys, list(out)))
+
+
+def max_active_clusters(split: int, smem_bytes: int) -> int:
+    out = ctypes.c_int(0)
+    check(lib.hfrk_max_active_clusters(split, smem_bytes, ctypes.byref(out)))
+    return out.value
 
 
 def device_status(clear: bool = True) -> Tuple[int, int]:

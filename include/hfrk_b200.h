@@ -181,6 +181,12 @@ int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* D, const fl
  * out[7]=tiles of 128 rows. Returns a status code. */
 int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8);
 
+/* How many clusters of `split` CTAs of the GEMM kernel with `smem_bytes` of dynamic shared memory
+ * the current device can hold at once (cudaOccupancyMaxActiveClusters): the figure the launch
+ * heuristic needs, exposed for tuning scripts. Clusters must fit inside one GPC, so the answer
+ * depends on how the SMs of this particular chip are spread over its GPCs. */
+int hfrk_max_active_clusters(int split, int smem_bytes, int* clusters_out);
+
 /* Device-side status word of the current device: 0, or the HFRK_DEVICE_TIMEOUT details packed
  * as (code << 24 | role << 16 | block index & 0xffff). Reads it with a synchronous copy, and
  * clears it when `clear` is non-zero. Kernels only ever write it when a bounded wait runs out. */
