@@ -577,6 +577,33 @@ struct Plan {
 
 int round_up(int v, int to) { return (v + to - 1) / to * to; }
 
+// Per-process tuning table: (padded tokens, n, k) -> (split, stages), filled by hfrk_tuning_set
+// from the output of the grid search. Chips differ in how their SMs are spread over the GPCs, so
+// the best cluster shape of a given projection can differ from one B200 to the next; the table
+// lets a deployment pin what its own sweep found. Consulted before the built-in rule.
+struct TuneKey {
+    int m_pad, n, k;
+    bool operator==(const TuneKey& o) const { return m_pad == o.m_pad && n == o.n && k == o.k; }
+};
+struct TuneKeyHash {
+    size_t operator()(const TuneKey& t) const {
+        return static_cast<size_t>(t.m_pad) * 1000003u ^ static_cast<size_t>(t.n) * 7919u ^ static_cast<size_t>(t.k) * 104729u;
+    }
+};
+struct TuneValue {
+    int split, stages;
+};
+std::mutex g_tune_mutex;
+std::unordered_map<TuneKey, TuneValue, TuneKeyHash> g_tune_table;
+
+bool tuning_lookup(int m_pad, int n, int k, TuneValue* out) {
+    std::lock_guard<std::mutex> lock(g_tune_mutex);
+    auto it = g_tune_table.find(TuneKey{m_pad, n, k});
+    if (it == g_tune_table.end()) return false;
+    *out = it->second;
+    return true;
+}
+
 // Launch shape of the cluster kernel for one launch of m <= kMaxMPad tokens, from sweeps on B200
 // (148 SMs) over the Llama-3 8B/70B projection shapes and their 2/4/8-way N and K shards:
 //   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream, and two small
@@ -598,6 +625,11 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     const int stage_bytes = kWStageBytes + m_pad * kBlockK;
     constexpr int kResidentTarget = 280;
 
+    TuneValue tuned;
+    if (split_req == 0 && stages_req == 0 && tuning_lookup(m_pad, n, k, &tuned)) {
+        split_req = tuned.split;
+        stages_req = tuned.stages;
+    }
     int split = split_req;
     if (split == 0) {
         split = kResidentTarget / tiles;
@@ -1231,6 +1263,26 @@ extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split
     if (rc != HFRK_SUCCESS) return rc;
     out8[0] = variant; out8[1] = 0; out8[2] = plan.stages; out8[3] = plan.grid;
     out8[4] = plan.smem_bytes; out8[5] = plan.m_pad; out8[6] = plan.nkb; out8[7] = plan.tiles;
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages) {
+    if (m <= 0 || n <= 0 || k <= 0 || split_k < 0 || split_k > hfrk::kMaxSplit || num_stages < 0 || num_stages == 1 ||
+        num_stages > hfrk::kMaxStages)
+        return HFRK_INVALID_CONFIG;
+    const int m_pad = hfrk::round_up(m > hfrk::kMaxMPad ? hfrk::kMaxMPad : m, 16);
+    std::lock_guard<std::mutex> lock(hfrk::g_tune_mutex);
+    if (split_k == 0 && num_stages == 0) {
+        hfrk::g_tune_table.erase(hfrk::TuneKey{m_pad, n, k});
+    } else {
+        hfrk::g_tune_table[hfrk::TuneKey{m_pad, n, k}] = hfrk::TuneValue{split_k, num_stages};
+    }
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_tuning_clear(void) {
+    std::lock_guard<std::mutex> lock(hfrk::g_tune_mutex);
+    hfrk::g_tune_table.clear();
     return HFRK_SUCCESS;
 }
 

@@ -30,7 +30,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_device_status", "hfrk_last_error", "hfrk_version", "hfrk_skinny_gemm_fp8_profile",
     "hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect", "hfrk_rowpar_connect_pointers",
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
-    "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters",
+    "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
 )
 
 
@@ -73,6 +73,9 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_device_status.argtypes = [i32, ctypes.POINTER(ctypes.c_uint)]
     lib.hfrk_max_active_clusters.argtypes = [i32, i32, ctypes.POINTER(i32)]
     lib.hfrk_max_active_clusters.restype = i32
+    lib.hfrk_tuning_set.argtypes = [i32, i32, i32, i32, i32]
+    lib.hfrk_tuning_set.restype = i32
+    lib.hfrk_tuning_clear.restype = i32
     lib.hfrk_last_error.restype = ctypes.c_char_p
     for name in ("hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
                  "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan", "hfrk_device_status", "hfrk_version"):

@@ -16,6 +16,9 @@ import torch
 from torch import Tensor
 
 from .binding import _skinny_gemm
+from .tuning import load_from_environment
+
+load_from_environment()  # HFRK_TUNING_FILE: per-shape launch shapes from the grid search
 
 _FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e4m3fnuz)
 _OUT_DTYPES = (torch.float16, torch.bfloat16)

@@ -181,6 +181,14 @@ int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* D, const fl
  * out[7]=tiles of 128 rows. Returns a status code. */
 int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8);
 
+/* Pins the launch shape of (m, n, k) for every later automatic call in this process: split_k and
+ * num_stages as in hfrk_skinny_gemm_fp8_ex (0 = leave that one to the built-in rule; both 0 = drop
+ * the entry). Token counts share an entry per multiple of 16. Fed from the JSON the grid search
+ * writes (hf_rocm_kernels/benchmarks/skinny_gemm/grid_search.py); stands where the reference has
+ * its hard-coded per-shape table (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:42-102). */
+int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages);
+int hfrk_tuning_clear(void);
+
 /* How many clusters of `split` CTAs of the GEMM kernel with `smem_bytes` of dynamic shared memory
  * the current device can hold at once (cudaOccupancyMaxActiveClusters): the figure the launch
  * heuristic needs, exposed for tuning scripts. Clusters must fit inside one GPC, so the answer

@@ -68,6 +68,30 @@ def test_plan_covers_the_sms(capi):
     assert capi.plan(4, 128, 256, capi.VARIANT_STREAMK)["ctas"] == 2
 
 
+def test_tuning_table_overrides_the_rule_per_shape(capi, tmp_path):
+    import json
+
+    from hf_rocm_kernels.operators.skinny_gemm import tuning
+
+    base = capi.plan(16, 4096, 4096)
+    path = tmp_path / "tuning.json"
+    path.write_text(json.dumps({"entries": [{"m": 16, "n": 4096, "k": 4096, "split_k": 4, "num_stages": 6},
+                                            {"m": 16, "n": 0, "k": 4096, "split_k": 4, "num_stages": 6}]}))
+    try:
+        assert tuning.load_tuning(str(path)) == 1                       # the malformed entry is refused
+        pinned = capi.plan(16, 4096, 4096)
+        assert (pinned["split_k"], pinned["num_stages"]) == (4, 6)
+        assert capi.plan(3, 4096, 4096)["split_k"] == 4                  # token counts share an entry per 16
+        assert capi.plan(17, 4096, 4096)["split_k"] == capi.plan(17, 4096, 4096, capi.VARIANT_CLUSTER, 0)["split_k"]
+        assert capi.plan(16, 4096, 4096, capi.VARIANT_CLUSTER, 2)["split_k"] == 2   # an explicit request still wins
+        assert capi.plan(16, 6144, 4096) == capi.plan(16, 6144, 4096)
+        assert capi.lib.hfrk_tuning_set(16, 4096, 4096, 0, 0) == 0       # drop the entry
+        assert capi.plan(16, 4096, 4096) == base
+        assert capi.lib.hfrk_tuning_set(16, 4096, 4096, 17, 4) == 6
+    finally:
+        tuning.clear_tuning()
+
+
 def test_plan_rejects_bad_arguments(capi):
     out = (ctypes.c_int * 8)()
     assert capi.lib.hfrk_skinny_gemm_plan(0, 128, 128, 0, 0, 0, out) == 6

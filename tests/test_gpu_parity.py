@@ -204,6 +204,23 @@ def test_every_launch_shape_gives_the_same_answer(capi, dev, checker, kw):
         assert torch.equal(out, again)
 
 
+def test_tuning_entry_changes_the_launch_not_the_result(capi, dev, checker):
+    from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
+    from hf_rocm_kernels.operators.skinny_gemm import tuning
+
+    case = wl.Case(8, 90, "tuned", 16, 4096, 4096, bias=True)
+    a, w, s, d_in, scale = _case_on_device(case, dev)
+    before = _run_c(capi, a, w, s, d_in, case.m, case.n)
+    try:
+        assert tuning.apply_tuning([{"m": 16, "n": 4096, "k": 4096, "split_k": 3, "num_stages": 5}]) == 1
+        assert capi.plan(16, 4096, 4096)["split_k"] == 3
+        tuned = _run_c(capi, a, w, s, d_in, case.m, case.n)
+    finally:
+        tuning.clear_tuning()
+    checker(before, a, w, scale, d_in, "untuned")
+    checker(tuned, a, w, scale, d_in, "tuned")
+
+
 @pytest.mark.parametrize("m", [64, 65, 70, 130])
 def test_token_counts_above_one_launch(capi, dev, checker, m):
     from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
