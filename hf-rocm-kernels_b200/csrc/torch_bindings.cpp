@@ -1,6 +1,6 @@
-// Registers torch.ops._HFRK_C.skinny_gemm_tb with the schema of the reference
-// (csrc/torch_bindings.cpp:38-41 of huggingface/hf-rocm-kernels) and forwards to the C ABI of
-// libhfrk_b200.so. This file is the only place where torch types meet the kernel library; it
+// Registers torch.ops._HFRK_C.skinny_gemm_tb, .swiglu and .residual_rms with the schemas of the
+// reference (csrc/torch_bindings.cpp:24-41 of huggingface/hf-rocm-kernels) and forwards to the C ABI
+// of libhfrk_b200.so. This file is the only place where torch types meet the kernel library; it
 // does what csrc/op_src/skinny_gemm/skinny_gemm_binding.cu:16-42 does in the reference: pull
 // pointers, shapes and the W pitch out of the tensors, pick the current stream of A's device and
 // return the launcher's status code.
@@ -58,7 +58,88 @@ int64_t skinny_gemm_tb(torch::Tensor& A, torch::Tensor& B, torch::Tensor& D, tor
                                 /*accumulate=*/1, static_cast<int>(split_k > 16 ? 16 : split_k), stream);
 }
 
+// gate_up [rows, 2*hidden] fp16/bf16 -> output [rows, hidden] fp8 (e4m3fnuz as in the reference, or
+// e4m3fn), next_buffer [rows, any] 16-bit zeroed. Stands where the reference has
+// csrc/op_src/swiglu/swiglu_dispatch.cu:8-42. num_threads belonged to the reference's launch and is
+// ignored; force_scalar selects the element-by-element kernel as it does there.
+void swiglu(torch::Tensor& gate_up, torch::Tensor& scale_tensor, torch::Tensor& output, torch::Tensor& next_buffer,
+            int64_t num_threads, bool force_scalar) {
+    (void)num_threads;
+    TORCH_CHECK(gate_up.dim() == 2 && gate_up.size(1) % 2 == 0 && gate_up.is_contiguous(),
+                "swiglu: gate_up must be a contiguous [rows, 2*hidden] matrix");
+    const int64_t rows = gate_up.size(0), hidden = gate_up.size(1) / 2;
+    TORCH_CHECK(output.is_contiguous() && output.numel() == rows * hidden, "swiglu: output must be [rows, hidden]");
+    TORCH_CHECK(next_buffer.is_contiguous() && next_buffer.element_size() == 2 &&
+                    (next_buffer.numel() == 0 || next_buffer.size(0) == rows),
+                "swiglu: next_buffer must be a contiguous 16-bit [rows, .] matrix");
+    TORCH_CHECK(scale_tensor.numel() == 1 && scale_tensor.scalar_type() == at::ScalarType::Float,
+                "swiglu: scale_tensor must hold one fp32");
+    const int in_kind = out_kind_of(gate_up), out_kind = fp8_kind_of(output);
+    TORCH_CHECK(in_kind >= 0, "swiglu: gate_up must be fp16 or bf16");
+    TORCH_CHECK(out_kind >= 0, "swiglu: output must be float8_e4m3fnuz or float8_e4m3fn");
+    TORCH_CHECK(rows <= INT32_MAX && hidden <= INT32_MAX, "swiglu: extent above 2^31");
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(gate_up));
+    const cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const int64_t buffer_cols = rows == 0 ? 0 : next_buffer.numel() / rows;
+    const int status = hfrk_swiglu_fp8(gate_up.data_ptr(), static_cast<const float*>(scale_tensor.data_ptr()),
+                                       output.data_ptr(), next_buffer.data_ptr(), static_cast<int>(rows),
+                                       static_cast<int>(hidden), buffer_cols, in_kind, out_kind,
+                                       force_scalar ? 1 : 0, stream);
+    TORCH_CHECK(status == HFRK_SUCCESS, "swiglu: status ", status, " (", hfrk_last_error(), ")");
+}
+
+// input, residual [rows, cols] and weight [cols] fp16/bf16; residual updated in place; output fp8
+// (scale_tensor defined) or the 16-bit type (scale_tensor undefined, i.e. None in Python);
+// next_buffer zeroed. Stands where the reference has
+// csrc/op_src/residual_rms/residual_rms_dispatch.cu:8-63.
+void residual_rms(torch::Tensor& input, torch::Tensor& residual, torch::Tensor& weight, torch::Tensor& scale_tensor,
+                  double epsilon, torch::Tensor& output, torch::Tensor& next_buffer, int64_t num_threads,
+                  bool force_scalar) {
+    TORCH_CHECK(input.dim() == 2 && input.is_contiguous() && residual.is_contiguous() && weight.is_contiguous() &&
+                    residual.sizes() == input.sizes() && weight.numel() == input.size(1),
+                "residual_rms: input and residual must be contiguous [rows, cols], weight [cols]");
+    const int dtype = out_kind_of(input);
+    TORCH_CHECK(dtype >= 0 && residual.scalar_type() == input.scalar_type() &&
+                    weight.scalar_type() == input.scalar_type(),
+                "residual_rms: input, residual and weight must share fp16 or bf16");
+    const int64_t rows = input.size(0), cols = input.size(1);
+    TORCH_CHECK(output.is_contiguous() && output.numel() == rows * cols, "residual_rms: output must be [rows, cols]");
+    TORCH_CHECK(next_buffer.is_contiguous() && next_buffer.element_size() == 2 &&
+                    (next_buffer.numel() == 0 || next_buffer.size(0) == rows),
+                "residual_rms: next_buffer must be a contiguous 16-bit [rows, .] matrix");
+    int out_kind;
+    const float* scale_ptr = nullptr;
+    if (output.scalar_type() == input.scalar_type()) {
+        out_kind = HFRK_OUT_SAME;
+    } else {
+        const int fp8 = fp8_kind_of(output);
+        TORCH_CHECK(fp8 >= 0, "residual_rms: output must be the input's dtype, float8_e4m3fnuz or float8_e4m3fn");
+        TORCH_CHECK(scale_tensor.defined() && scale_tensor.numel() == 1 &&
+                        scale_tensor.scalar_type() == at::ScalarType::Float,
+                    "residual_rms: an fp8 output needs a one-element fp32 scale_tensor");
+        out_kind = fp8 == HFRK_E4M3FNUZ ? HFRK_OUT_E4M3FNUZ : HFRK_OUT_E4M3FN;
+        scale_ptr = static_cast<const float*>(scale_tensor.data_ptr());
+    }
+    TORCH_CHECK(rows <= INT32_MAX && cols <= INT32_MAX, "residual_rms: extent above 2^31");
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(input));
+    const cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const int64_t buffer_cols = rows == 0 ? 0 : next_buffer.numel() / rows;
+    const int status = hfrk_residual_rms(input.data_ptr(), residual.data_ptr(), weight.data_ptr(), scale_ptr,
+                                         static_cast<float>(epsilon), output.data_ptr(), next_buffer.data_ptr(),
+                                         static_cast<int>(rows), static_cast<int>(cols), buffer_cols, dtype, out_kind,
+                                         static_cast<int>(num_threads), force_scalar ? 1 : 0, stream);
+    TORCH_CHECK(status == HFRK_SUCCESS, "residual_rms: status ", status, " (", hfrk_last_error(), ")");
+}
+
 TORCH_LIBRARY(_HFRK_C, ops) {
+    ops.def(
+        "residual_rms(Tensor input, Tensor! residual, Tensor weight, Tensor scale_tensor, float epsilon, Tensor! "
+        "output, Tensor! next_buffer, int num_threads, bool force_scalar) -> ()");
+    ops.impl("residual_rms", torch::kCUDA, &residual_rms);
+    ops.def(
+        "swiglu(Tensor gate_up, Tensor scale_tensor, Tensor! output, Tensor! next_buffer, int num_threads, "
+        "bool force_scalar) -> ()");
+    ops.impl("swiglu", torch::kCUDA, &swiglu);
     ops.def(
         "skinny_gemm_tb(Tensor A, Tensor B, Tensor! D, Tensor scale_tensor, int split_k, int A_producers, "
         "int B_producers, int consumers, int a_lanes, int b_lanes, int qsize, int op_m, int ops) -> int");

@@ -16,6 +16,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 E4M3FN, E4M3FNUZ = 0, 1
 F16, BF16, F32 = 0, 1, 2
 VARIANT_AUTO, VARIANT_CLUSTER, VARIANT_STREAMK = 0, 1, 2
+OUT_SAME, OUT_E4M3FN, OUT_E4M3FNUZ = 0, 1, 2
 
 STATUS_NAMES = {
     0: "SUCCESS", 1: "M_ABOVE_WARPTILE_M", 2: "N_NOT_EVEN", 3: "K_NOT_DIVISIBLE", 4: "TOO_MANY_WARPS",
@@ -31,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect", "hfrk_rowpar_connect_pointers",
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
+    "hfrk_swiglu_fp8", "hfrk_residual_rms",
 )
 
 
@@ -76,6 +78,10 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_tuning_set.argtypes = [i32, i32, i32, i32, i32]
     lib.hfrk_tuning_set.restype = i32
     lib.hfrk_tuning_clear.restype = i32
+    lib.hfrk_swiglu_fp8.argtypes = [vp, vp, vp, vp, i32, i32, i64, i32, i32, i32, vp]
+    lib.hfrk_swiglu_fp8.restype = i32
+    lib.hfrk_residual_rms.argtypes = [vp, vp, vp, vp, ctypes.c_float, vp, vp, i32, i32, i64, i32, i32, i32, i32, vp]
+    lib.hfrk_residual_rms.restype = i32
     lib.hfrk_last_error.restype = ctypes.c_char_p
     for name in ("hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
                  "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan", "hfrk_device_status", "hfrk_version"):
@@ -178,6 +184,34 @@ def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True
             a_host.data_ptr(), w_dev.data_ptr(), d_host.data_ptr(), scale_dev.data_ptr(), m, n, k, w_dev.stride(0),
             fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype), out_kind(d_host.dtype), int(accumulate),
             work_dev.data_ptr(), _stream_ptr(stream, w_dev.device))
+
+
+def swiglu(gate_up: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, next_buffer: Optional[torch.Tensor] = None,
+           force_scalar: bool = False, stream=None) -> int:
+    """hfrk_swiglu_fp8 on torch tensors: gate_up [rows, 2*hidden] 16-bit, out [rows, hidden] fp8."""
+    rows, two_hidden = gate_up.shape
+    assert gate_up.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (rows, two_hidden // 2)
+    buffer_cols = 0 if next_buffer is None or rows == 0 else next_buffer.numel() // rows
+    return lib.hfrk_swiglu_fp8(gate_up.data_ptr(), scale.data_ptr(), out.data_ptr(),
+                               0 if next_buffer is None else next_buffer.data_ptr(), rows, two_hidden // 2,
+                               buffer_cols, out_kind(gate_up.dtype), fp8_kind(out.dtype), int(force_scalar),
+                               _stream_ptr(stream, gate_up.device))
+
+
+def residual_rms(input: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],
+                 epsilon: float, output: torch.Tensor, next_buffer: Optional[torch.Tensor] = None,
+                 num_threads: int = 0, force_scalar: bool = False, stream=None) -> int:
+    """hfrk_residual_rms on torch tensors; the output kind follows ``output.dtype``."""
+    rows, cols = input.shape
+    assert input.is_contiguous() and residual.is_contiguous() and weight.is_contiguous() and output.is_contiguous()
+    kind = OUT_SAME if output.dtype == input.dtype else (OUT_E4M3FNUZ if fp8_kind(output.dtype) == E4M3FNUZ
+                                                         else OUT_E4M3FN)
+    buffer_cols = 0 if next_buffer is None or rows == 0 else next_buffer.numel() // rows
+    return lib.hfrk_residual_rms(input.data_ptr(), residual.data_ptr(), weight.data_ptr(),
+                                 0 if scale is None else scale.data_ptr(), epsilon, output.data_ptr(),
+                                 0 if next_buffer is None else next_buffer.data_ptr(), rows, cols, buffer_cols,
+                                 out_kind(input.dtype), kind, num_threads, int(force_scalar),
+                                 _stream_ptr(stream, input.device))
 
 
 def plan(m: int, n: int, k: int, variant: int = VARIANT_AUTO, split_k: int = 0, ctas_per_sm: int = 0) -> dict:

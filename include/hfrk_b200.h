@@ -1,7 +1,7 @@
 /*
  * hfrk_b200.h - C ABI of the B200 (sm_100a) FP8 skinny GEMM library, libhfrk_b200.so.
  *
- * One operation:   D[m,n] <- (accumulate ? D_in[m,n] : 0) + scale * sum_k A[m,k] * W[n,k]
+ * The GEMM:        D[m,n] <- (accumulate ? D_in[m,n] : 0) + scale * sum_k A[m,k] * W[n,k]
  *   A  [M,K]  fp8 e4m3, row-major, contiguous
  *   W  [N,K]  fp8 e4m3, row-major with a row stride of w_row_stride elements
  *   D  [M,N]  fp16 or bf16, row-major, contiguous, updated in place
@@ -15,7 +15,9 @@
  *   csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:21-71    (validation, grid/block, dispatch)
  *   csrc/op_src/skinny_gemm/skinny_gemm_kernel.cu:6-79     (the device kernel)
  * and keep its convention of returning a status int instead of throwing
- * (csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:9-17).
+ * (csrc/op_src/skinny_gemm/skinny_gemm_caller.cu:9-17). The two element-wise kernels that sit
+ * between the GEMMs of a decoder layer (hfrk_residual_rms, hfrk_swiglu_fp8) are declared further
+ * down with the reference files they replace.
  */
 #ifndef HFRK_B200_H_
 #define HFRK_B200_H_
@@ -180,6 +182,48 @@ int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* D, const fl
  * out[4]=dynamic shared memory bytes, out[5]=padded token count (MMA N), out[6]=K blocks of 128,
  * out[7]=tiles of 128 rows. Returns a status code. */
 int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8);
+
+/* ---- the element-wise kernels either side of the GEMM in a decoder layer -------------------
+ * Both quantise the input of the next projection to fp8 and zero the buffer that projection
+ * accumulates into (the GEMM computes D += ...), so a layer is GEMM, one of these, GEMM, ...
+ * with nothing in between. Both are launched as programmatic dependents (unless HFRK_PDL=0):
+ * the weight prefetch of the GEMM after them overlaps them.
+ *
+ * Output encodings. HFRK_OUT_E4M3FNUZ writes the bytes the reference writes: value / scale in
+ * e4m3fnuz, where callers pass the DOUBLED scale of hf_rocm_kernels/utils/fp8.py:31-33. The
+ * bytes saturate at +-224 (0x7e), as utils/fp8.py:19-20 clamps, not at the +-240 (0x7f) of the
+ * HIP conversion: 0x7f is NaN to a consumer that multiplies the bytes natively as e4m3fn, as the
+ * GEMM here does. Negative zero is written as 0x00 (utils/fp8.py:26-30). HFRK_OUT_E4M3FN writes
+ * value / scale in e4m3fn, saturating at +-448. */
+enum hfrk_norm_out { HFRK_OUT_SAME = 0, HFRK_OUT_E4M3FN = 1, HFRK_OUT_E4M3FNUZ = 2 };
+
+/* out[r, c] = fp8( silu(gate_up[r, c]) * gate_up[r, hidden + c] / scale ),  c < hidden;
+ * next_buffer[rows, buffer_cols] (16-bit elements) <- 0.
+ *   gate_up [rows, 2*hidden] fp16 or bf16 (in_dtype: enum hfrk_out_dtype), contiguous
+ *   out     [rows, hidden]   one byte per element, out_kind HFRK_E4M3FN or HFRK_E4M3FNUZ
+ *   scale_dev                one fp32 on the device
+ * hidden % 8 == 0 with gate_up 16-byte and out 8-byte aligned takes 16-byte loads; anything else
+ * (or force_scalar != 0) takes the element-by-element kernel. rows == 0 is a no-op.
+ * Replaces swiglu() of the reference (csrc/op_src/swiglu/swiglu_dispatch.cu:8-42; op schema
+ * csrc/torch_bindings.cpp:31-35). */
+int hfrk_swiglu_fp8(const void* gate_up, const float* scale_dev, void* out, void* next_buffer,
+                    int rows, int hidden, int64_t buffer_cols, int in_dtype, int out_kind,
+                    int force_scalar, void* stream);
+
+/* residual <- input + residual (in place, rounded to the 16-bit type);
+ * output <- residual * rsqrt(mean(residual^2) + epsilon) * weight, written in the 16-bit type
+ * (out_kind HFRK_OUT_SAME, scale_dev may be NULL) or divided by *scale_dev and written as fp8
+ * (HFRK_OUT_E4M3FN / HFRK_OUT_E4M3FNUZ); next_buffer[rows, buffer_cols] (16-bit elements) <- 0.
+ *   input, residual [rows, cols], weight [cols]: fp16 or bf16 (dtype: enum hfrk_out_dtype)
+ *   num_threads : CTA size, a multiple of 32 in [32, 1024]; anything else lets the library choose
+ * One CTA per row. cols % 8 == 0 with 16-byte aligned tensors takes 16-byte loads; anything else
+ * (or force_scalar != 0) the element-by-element kernel. rows == 0 is a no-op.
+ * Replaces residual_rms() of the reference (csrc/op_src/residual_rms/residual_rms_dispatch.cu:8-63;
+ * op schema csrc/torch_bindings.cpp:25-29). */
+int hfrk_residual_rms(const void* input, void* residual, const void* weight, const float* scale_dev,
+                      float epsilon, void* output, void* next_buffer, int rows, int cols,
+                      int64_t buffer_cols, int dtype, int out_kind, int num_threads, int force_scalar,
+                      void* stream);
 
 /* Pins the launch shape of (m, n, k) for every later automatic call in this process: split_k and
  * num_stages as in hfrk_skinny_gemm_fp8_ex (0 = leave that one to the built-in rule; both 0 = drop

@@ -35,6 +35,7 @@ def test_library_exports_every_declared_symbol(capi):
 def test_header_cites_the_reference_for_each_entry_point():
     text = open(HEADER).read()
     assert "skinny_gemm_binding.cu:16-42" in text and "skinny_gemm_caller.cu" in text
+    assert "swiglu_dispatch.cu:8-42" in text and "residual_rms_dispatch.cu:8-63" in text
     assert "torch" not in re.sub(r"/\*.*?\*/", "", text, flags=re.S)  # no torch types in signatures
 
 
@@ -121,6 +122,29 @@ def test_argument_validation_happens_before_any_cuda_call(capi):
     assert capi.lib.hfrk_skinny_gemm_fp8_simt(*base, 4, 128, 250, 256, 0, 0, 0, 1, None) == 3
     assert capi.lib.hfrk_host_call_workspace_bytes(4, 128, 256) == 1024 + 2048
     assert capi.lib.hfrk_host_call_workspace_bytes(0, 128, 256) == 0
+
+
+def test_elementwise_argument_validation_happens_before_any_cuda_call(capi):
+    x = torch.zeros((2, 64), dtype=torch.float16)
+    w = torch.ones(64, dtype=torch.float16)
+    out = torch.zeros((2, 64), dtype=torch.uint8)
+    s = torch.ones(1, dtype=torch.float32)
+    swiglu = capi.lib.hfrk_swiglu_fp8
+    assert swiglu(x.data_ptr(), s.data_ptr(), out.data_ptr(), None, 0, 32, 0, capi.F16, capi.E4M3FN, 0, None) == 0
+    assert swiglu(x.data_ptr(), s.data_ptr(), out.data_ptr(), None, 2, 32, 0, capi.F32, capi.E4M3FN, 0, None) == 8
+    assert swiglu(x.data_ptr(), s.data_ptr(), out.data_ptr(), None, 2, 32, 0, capi.F16, 3, 0, None) == 8
+    assert swiglu(x.data_ptr(), None, out.data_ptr(), None, 2, 32, 0, capi.F16, capi.E4M3FN, 0, None) == 6
+    assert swiglu(x.data_ptr(), s.data_ptr(), out.data_ptr(), None, 2, 32, 16, capi.F16, capi.E4M3FN, 0, None) == 6
+    assert swiglu(x.data_ptr() + 1, s.data_ptr(), out.data_ptr(), None, 2, 16, 0, capi.F16, capi.E4M3FN, 0, None) == 7
+    rms = capi.lib.hfrk_residual_rms
+    ptrs = (x.data_ptr(), x.data_ptr(), w.data_ptr())
+    assert rms(*ptrs, None, 1e-5, out.data_ptr(), None, 0, 64, 0, capi.F16, capi.OUT_SAME, 0, 0, None) == 0
+    assert rms(*ptrs, None, -1.0, out.data_ptr(), None, 2, 64, 0, capi.F16, capi.OUT_SAME, 0, 0, None) == 6
+    assert rms(*ptrs, None, 1e-5, out.data_ptr(), None, 2, 64, 0, capi.F16, capi.OUT_E4M3FNUZ, 0, 0, None) == 6
+    assert rms(*ptrs, None, 1e-5, out.data_ptr(), None, 2, 64, 0, capi.F32, capi.OUT_SAME, 0, 0, None) == 8
+    assert rms(*ptrs, None, 1e-5, out.data_ptr(), None, 2, 64, 0, capi.F16, 3, 0, 0, None) == 8
+    assert rms(x.data_ptr() + 1, *ptrs[1:], None, 1e-5, out.data_ptr(), None, 2, 32, 0, capi.F16, capi.OUT_SAME, 0, 0,
+               None) == 7
 
 
 def test_status_names_cover_the_header(capi):

@@ -41,6 +41,105 @@ def test_op_schema_is_the_reference_schema(pkg):
     assert schema.arguments[2].alias_info is not None and schema.arguments[2].alias_info.is_write
 
 
+def test_elementwise_operators_keep_the_reference_surface(pkg):
+    """Names, argument order and op schemas of swiglu and residual_rms
+    (reference: hf_rocm_kernels/__init__.py:1-6, operators/*/wrapped.py, csrc/torch_bindings.cpp:24-35)."""
+    from hf_rocm_kernels.combined_ops import llama_mlp_combined_ops
+    from hf_rocm_kernels.operators.residual_rms import (generate_residual_rms_data, precise_residual_rms,
+                                                         reference_residual_rms, residual_rms)
+    from hf_rocm_kernels.operators.residual_rms.binding import _residual_rms
+    from hf_rocm_kernels.operators.swiglu import generate_swiglu_data, reference_swiglu, swiglu
+    from hf_rocm_kernels.operators.swiglu.binding import _swiglu
+
+    assert pkg.swiglu is swiglu and pkg.residual_rms is residual_rms
+    assert set(pkg.__all__) == {"residual_rms", "swiglu", "skinny_gemm"}
+    assert list(inspect.signature(swiglu).parameters)[:5] == [
+        "gate_up_proj", "scale_tensor", "next_buffer", "force_scalar", "num_threads"]
+    assert list(inspect.signature(_swiglu).parameters) == [
+        "gate_up_proj", "scale_tensor", "swiglu_out", "next_buffer", "num_threads", "force_scalar"]
+    assert list(inspect.signature(reference_swiglu).parameters) == ["gate_up_proj", "scale_tensor", "next_buffer"]
+    assert list(inspect.signature(generate_swiglu_data).parameters)[:4] == ["rows", "hidden_dim", "buffer_cols", "seed"]
+    assert list(inspect.signature(residual_rms).parameters)[:8] == [
+        "input", "residual", "weight", "epsilon", "scale_tensor", "next_buffer", "num_threads", "force_scalar"]
+    assert list(inspect.signature(_residual_rms).parameters) == [
+        "input", "residual", "weight", "scale_tensor", "epsilon", "output", "next_buffer", "num_threads",
+        "force_scalar"]
+    for fn in (reference_residual_rms, precise_residual_rms):
+        assert list(inspect.signature(fn).parameters) == [
+            "input", "residual", "weight", "epsilon", "scale_tensor", "next_buffer"]
+    assert list(inspect.signature(generate_residual_rms_data).parameters)[:5] == [
+        "rows", "cols", "buffer_cols", "dtype", "seed"]
+    assert list(inspect.signature(llama_mlp_combined_ops).parameters)[:12] == [
+        "attn_output", "residual", "rms_weight", "rms_epsilon", "gate_up_weight", "gate_up_input_scale",
+        "gate_up_output_scale", "down_weight", "down_input_scale", "down_output_scale", "gate_up_gemm_hp",
+        "down_gemm_hp"]
+
+    for name, text in (
+        ("residual_rms", "_HFRK_C::residual_rms(Tensor input, Tensor! residual, Tensor weight, Tensor scale_tensor, "
+                         "float epsilon, Tensor! output, Tensor! next_buffer, int num_threads, bool force_scalar) -> ()"),
+        ("swiglu", "_HFRK_C::swiglu(Tensor gate_up, Tensor scale_tensor, Tensor! output, Tensor! next_buffer, "
+                   "int num_threads, bool force_scalar) -> ()"),
+    ):
+        schema = getattr(torch.ops._HFRK_C, name).default._schema
+        assert str(schema) == str(torch._C.parse_schema(text))
+
+
+def test_elementwise_references_agree_with_the_oracle_on_cpu(pkg, oracle_mod):
+    """The package's torch statements (used by the GPU tests as the reference's criteria) against
+    the numpy oracle, which is pinned to the reference's outputs."""
+    import numpy as np
+
+    import elementwise_oracle as ew
+    from hf_rocm_kernels.operators.residual_rms import (generate_residual_rms_data, precise_residual_rms,
+                                                         reference_residual_rms)
+    from hf_rocm_kernels.operators.swiglu import generate_swiglu_data, reference_swiglu
+
+    f16 = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16).view(np.float16)
+    gate_up, scale, buf = generate_swiglu_data(5, 520, 24, seed=1, device="cpu")
+    buf.fill_(1)
+    got = reference_swiglu(gate_up, scale, buf).view(torch.uint8).numpy()
+    assert float(buf.abs().sum()) == 0
+    assert np.array_equal(got, ew.reference_swiglu(f16(gate_up), 2 * float(scale)))
+
+    x, res, w, eps, scale, _ = generate_residual_rms_data(4, 1024, 0, torch.float8_e4m3fnuz, seed=2, device="cpu")
+    out, new_res, doubled = reference_residual_rms(x.clone(), res.clone(), w, eps, scale)
+    expect, expect_res = ew.reference_residual_rms(f16(x), f16(res), f16(w), eps, 2 * float(scale), form="torch")
+    assert float(doubled) == 2 * float(scale)
+    assert np.array_equal(f16(new_res).view(np.uint16), expect_res.view(np.uint16))
+    assert (ew.fp8_step_distance(out.view(torch.uint8).numpy(), expect) != 0).mean() < 2e-3
+    precise, _ = precise_residual_rms(x.clone(), res.clone(), w, eps, scale)
+    expect_p = ew.precise_residual_rms(f16(x), f16(res), f16(w), eps, 2 * float(scale))
+    assert (ew.fp8_step_distance(precise.view(torch.uint8).numpy(), expect_p) != 0).mean() < 2e-3
+    out16, _, none = reference_residual_rms(x.clone(), res.clone(), w, eps, None)
+    assert none is None and out16.dtype == torch.float16
+
+
+def test_elementwise_checks(pkg):
+    from hf_rocm_kernels.operators.residual_rms.wrapped import infer_num_threads, residual_rms_checks
+    from hf_rocm_kernels.operators.swiglu.wrapped import swiglu_checks
+
+    g = torch.zeros((2, 64), dtype=torch.float16)
+    with pytest.raises(AssertionError, match="cuda"):
+        swiglu_checks(g, torch.ones(1), torch.empty((2, 0), dtype=torch.float16))
+    with pytest.raises(AssertionError, match="even"):
+        swiglu_checks(torch.zeros((2, 63), dtype=torch.float16), torch.ones(1), torch.empty((2, 0), dtype=torch.float16))
+    with pytest.raises(AssertionError, match="rows"):
+        swiglu_checks(g, torch.ones(1), torch.empty((3, 8), dtype=torch.float16))
+    x = torch.zeros((2, 64), dtype=torch.float16)
+    with pytest.raises(AssertionError, match="same shape"):
+        residual_rms_checks(x, torch.zeros((2, 32), dtype=torch.float16), torch.ones(64, dtype=torch.float16), None,
+                            1e-5, torch.empty((2, 0), dtype=torch.float16))
+    with pytest.raises(AssertionError, match="weight"):
+        residual_rms_checks(x, x, torch.ones(32, dtype=torch.float16), None, 1e-5,
+                            torch.empty((2, 0), dtype=torch.float16))
+    with pytest.raises(AssertionError, match="cuda"):
+        residual_rms_checks(x, x, torch.ones(64, dtype=torch.float16), None, 1e-5,
+                            torch.empty((2, 0), dtype=torch.float16))
+    with pytest.raises(ValueError):
+        infer_num_threads(4, 2048)
+    assert infer_num_threads(4, 0) == 0 and infer_num_threads(4, 512) == 512
+
+
 def test_checks_reject_what_the_reference_rejects(pkg):
     from hf_rocm_kernels.operators.skinny_gemm.wrapped import infer_skinny_gemm_params, skinny_gemm_checks
 
