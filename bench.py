@@ -261,6 +261,8 @@ def run_ours(args):
                            "hbm_tbps": round(c.algorithmic_bytes() / us / 1e6, 3),
                            "weight_tbps": round(c.weight_bytes / us / 1e6, 3)})
 
+    layer_block = mlp_block_detail(torch, dev) if world == 1 and not args.no_detail else None
+
     status_code, status_word = capi.device_status(clear=True)
     if status_code != 0:
         raise RuntimeError(f"device status word {status_word:#x}: a bounded wait ran out during the benchmark")
@@ -303,11 +305,54 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(torch, wl)
         if detail is not None:
             line["detail"] = detail
+        if layer_block is not None:
+            line["layer_block"] = layer_block
         if multi is not None:
             line["multi_gpu"] = multi
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def mlp_block_detail(torch, dev, tokens=16):
+    """The Llama-3-8B MLP block as the four-launch chain residual_rms -> gate/up GEMM -> swiglu ->
+    down GEMM (hf_rocm_kernels.combined_ops.llama_mlp_combined_ops), and the two element-wise
+    kernels on their own, each from a CUDA graph of back-to-back calls. Four weight sets rotate so
+    that weights come from HBM (4 x 176 MB >> L2). Not part of the headline figure."""
+    from hf_rocm_kernels.combined_ops import llama_mlp_combined_ops
+    from hf_rocm_kernels.utils.benchmarking import time_graph_us
+    from hf_rocm_kernels.utils.fp8 import fp8_quantize_e4m3fn
+
+    hidden, inter, sets = 4096, 14336, 4
+    gen = torch.Generator(device=dev).manual_seed(7)
+    attn = torch.randn(tokens, hidden, device=dev, generator=gen).bfloat16()
+    residual = torch.randn(tokens, hidden, device=dev, generator=gen).bfloat16()
+    rms_weight = torch.ones(hidden, device=dev).bfloat16()
+    gate_up = [fp8_quantize_e4m3fn(torch.randn(2 * inter, hidden, device=dev, generator=gen) * 0.02)
+               for _ in range(sets)]
+    down = [fp8_quantize_e4m3fn(torch.randn(hidden, inter, device=dev, generator=gen) * 0.02) for _ in range(sets)]
+    s_in = torch.tensor([4.0 / 448], device=dev)
+    s_act = torch.tensor([16.0 / 448], device=dev)
+    scales = [(s_in * gate_up[j][1], s_act * down[j][1]) for j in range(sets)]
+
+    def block(i):
+        j = i % sets
+        llama_mlp_combined_ops(attn, residual, rms_weight, 1e-5, gate_up[j][0].t(), s_in, scales[j][0],
+                               down[j][0].t(), s_act, scales[j][1])
+
+    chain_us = time_graph_us(block, graph_size=8, warmups=5, iterations=20)
+    normed = torch.empty(tokens, hidden, dtype=torch.float8_e4m3fn, device=dev)
+    gu = torch.zeros(tokens, 2 * inter, dtype=torch.bfloat16, device=dev)
+    act = torch.empty(tokens, inter, dtype=torch.float8_e4m3fn, device=dev)
+    out = torch.zeros(tokens, hidden, dtype=torch.bfloat16, device=dev)
+    rms_us = time_graph_us(lambda i: torch.ops._HFRK_C.residual_rms(attn, residual, rms_weight, s_in, 1e-5, normed,
+                                                                    gu, 0, False), 16, 5, 20)
+    swiglu_us = time_graph_us(lambda i: torch.ops._HFRK_C.swiglu(gu, s_act, act, out, 0, False), 16, 5, 20)
+    weight_bytes = 3 * inter * hidden
+    return {"block": "llama3-8b mlp, residual_rms -> gate_up -> swiglu -> down", "tokens": tokens,
+            "us_per_block": round(chain_us, 2), "weight_tbps": round(weight_bytes / chain_us / 1e6, 3),
+            "launches_per_block": 4, "residual_rms_alone_us": round(rms_us, 2),
+            "swiglu_alone_us": round(swiglu_us, 2)}
 
 
 def _graph_time_us(torch, dist, dev, fns, reps=20, warm=5):

@@ -55,13 +55,17 @@ static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
 
 // Row-parallel (K split over GPUs) exchange state, as seen by the kernel of ONE rank. Every rank
 // owns an exchange buffer that its peers write into over NVLink:
-//   cells : {fp32 partial sum, epoch} [2 parities][world sources][elems_per_src], 8 bytes each
+//   cells : {fp32 value, epoch} [2 parities][world + 1 sources][elems_per_src], 8 bytes each
 // A cell is written with ONE 8-byte store, so its reader sees value and epoch together: a cell
 // whose epoch equals the current call's is valid. No flag, no fence and no barrier is needed
 // between writer and reader. cells[p] is the base of rank p's buffer (p == rank: the local one).
+// Sources 0..world-1 hold the partial sums of those ranks; source `world` holds finished sums
+// sent back by the element's owner in the two-shot exchange.
 constexpr int kMaxWorld = 8;
+constexpr unsigned long long kTwoShotFromBytes = 1ull << 20;
 struct RowparDev {
     int rank, world;
+    int two_shot;               // set per launch: 0 = every rank sends its partials to every peer
     unsigned int elems_per_src;
     uint2* cells[kMaxWorld];
     unsigned int* call_index;   // local: number of completed calls on this communicator
@@ -105,20 +109,32 @@ __device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* ptr) {
     return v;
 }
 
-// One-shot all-reduce of the values this thread owns, fused into the GEMM epilogue. `val` holds
-// CNT partial sums, `slot[i]` the element's index in the exchange buffer (0xffffffff = unused).
-// The thread writes {value, epoch} cells into every peer's buffer (plain 8-byte stores to peer
-// memory: NVLink), then polls the matching cells of its own buffer until each carries this call's
-// epoch (bounded), and adds the `world` contributions in rank order, so that all ranks compute
-// bit-identical sums. Nothing here synchronises the CTA. Returns false if a peer did not deliver
-// in time (the status word is set).
+// All-reduce of the values this thread owns, fused into the GEMM epilogue. `val` holds CNT partial
+// sums, `slot[i]` the element's index in the exchange buffer (0xffffffff = unused). All ranks run
+// the same launch shape, so "this thread's element i" names the same output element on every rank.
+//
+// One-shot (rp.two_shot == 0): the thread writes {value, epoch} cells into every peer's buffer
+// (plain 8-byte stores to peer memory: NVLink), then polls the matching cells of its own buffer
+// until each carries this call's epoch, and adds the `world` contributions in rank order. One
+// NVLink crossing of latency; every rank sends (world - 1) copies of its partial tile.
+//
+// Two-shot (rp.two_shot != 0): each CTA position has an owner rank. The other ranks send their
+// partials to the owner only; the owner adds them in rank order and sends the finished sum to
+// every peer. Two crossings of latency, but 1/world of the one-shot's traffic for the partials
+// plus one copy of the result: the better trade once the partial tiles reach megabytes.
+//
+// Either way all ranks end with bit-identical sums. Nothing here synchronises the CTA; every wait
+// is bounded. Returns false if a peer did not deliver in time (the status word is set).
 template <int CNT>
 __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
                                                 float (&val)[CNT], volatile uint32_t* abort_flag) {
     const unsigned int parity = epoch & 1u;
-    const size_t my_src = static_cast<size_t>(parity * rp.world + rp.rank);
+    const size_t sources = static_cast<size_t>(rp.world) + 1;
+    const int owner = rp.two_shot ? static_cast<int>((blockIdx.x + blockIdx.y) % static_cast<unsigned>(rp.world)) : -1;
+    const bool gather = !rp.two_shot || owner == rp.rank;   // this thread adds up the ranks' partials
+    const size_t my_src = parity * sources + static_cast<size_t>(rp.rank);
     for (int peer = 0; peer < rp.world; ++peer) {
-        if (peer == rp.rank) continue;
+        if (peer == rp.rank || (rp.two_shot && peer != owner)) continue;
         uint2* dst = rp.cells[peer] + my_src * rp.elems_per_src;
 #pragma unroll
         for (int i = 0; i < CNT; ++i) {
@@ -131,47 +147,88 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
     constexpr int kBatch = 4;
     bool ok = true;
     const long long start = clock64();
+    const uint2* const mine = rp.cells[rp.rank] + parity * sources * rp.elems_per_src;
 #pragma unroll
     for (int i0 = 0; i0 < CNT; i0 += kBatch) {
         bool any = false;
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) any |= slot[i0 + b] != 0xffffffffu;
         if (!any || !ok) continue;
-        uint32_t got[kBatch][kMaxWorld];
-        for (;;) {
-            bool ready = true;
+        if (gather) {
+            uint32_t got[kBatch][kMaxWorld];
+            for (;;) {
+                bool ready = true;
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+#pragma unroll
+                    for (int src = 0; src < kMaxWorld; ++src) {
+                        got[b][src] = 0u;
+                        if (src < rp.world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
+                            const uint2 cell =
+                                ld_relaxed_sys_v2(mine + static_cast<size_t>(src) * rp.elems_per_src + slot[i0 + b]);
+                            got[b][src] = cell.x;
+                            ready &= cell.y == epoch;
+                        }
+                    }
+                }
+                if (ready) break;
+                if (*abort_flag || clock64() - start > kWaitLimitCycles) {
+                    *abort_flag = 1u;
+                    record_timeout(kRolePeer);
+                    ok = false;
+                    break;
+                }
+            }
+            if (!ok) continue;
 #pragma unroll
             for (int b = 0; b < kBatch; ++b) {
+                float sum = 0.0f;
 #pragma unroll
                 for (int src = 0; src < kMaxWorld; ++src) {
-                    got[b][src] = 0u;
-                    if (src < rp.world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
-                        const uint2 cell = ld_relaxed_sys_v2(rp.cells[rp.rank] +
-                                                             static_cast<size_t>(parity * rp.world + src) *
-                                                                 rp.elems_per_src +
-                                                             slot[i0 + b]);
-                        got[b][src] = cell.x;
-                        ready &= cell.y == epoch;
+                    if (src < rp.world) sum += (src == rp.rank) ? val[i0 + b] : __uint_as_float(got[b][src]);
+                }
+                val[i0 + b] = sum;
+            }
+            if (rp.two_shot) {
+                // the owner hands the finished sums to everyone else
+                const size_t fin = (parity * sources + static_cast<size_t>(rp.world)) * rp.elems_per_src;
+                for (int peer = 0; peer < rp.world; ++peer) {
+                    if (peer == rp.rank) continue;
+#pragma unroll
+                    for (int b = 0; b < kBatch; ++b) {
+                        if (slot[i0 + b] != 0xffffffffu)
+                            st_relaxed_sys_v2(rp.cells[peer] + fin + slot[i0 + b], __float_as_uint(val[i0 + b]), epoch);
                     }
                 }
             }
-            if (ready) break;
-            if (*abort_flag || clock64() - start > kWaitLimitCycles) {
-                *abort_flag = 1u;
-                record_timeout(kRolePeer);
-                ok = false;
-                break;
-            }
-        }
-        if (!ok) continue;
+        } else {
+            // not the owner: wait for the finished sums
+            const uint2* const fin = mine + static_cast<size_t>(rp.world) * rp.elems_per_src;
+            uint32_t got[kBatch];
+            for (;;) {
+                bool ready = true;
 #pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-            float sum = 0.0f;
-#pragma unroll
-            for (int src = 0; src < kMaxWorld; ++src) {
-                if (src < rp.world) sum += (src == rp.rank) ? val[i0 + b] : __uint_as_float(got[b][src]);
+                for (int b = 0; b < kBatch; ++b) {
+                    got[b] = 0u;
+                    if (slot[i0 + b] != 0xffffffffu) {
+                        const uint2 cell = ld_relaxed_sys_v2(fin + slot[i0 + b]);
+                        got[b] = cell.x;
+                        ready &= cell.y == epoch;
+                    }
+                }
+                if (ready) break;
+                if (*abort_flag || clock64() - start > kWaitLimitCycles) {
+                    *abort_flag = 1u;
+                    record_timeout(kRolePeer);
+                    ok = false;
+                    break;
+                }
             }
-            val[i0 + b] = sum;
+            if (!ok) continue;
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                if (slot[i0 + b] != 0xffffffffu) val[i0 + b] = __uint_as_float(got[b]);
+            }
         }
     }
     return ok;
@@ -864,7 +921,8 @@ int launch_streamk(const void* A, const void* W, void* D, const float* scale_dev
 int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, int m, int n, int k,
                 int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int variant,
                 int split_req, int ctas_per_sm, int stages_req, int use_pdl, cudaStream_t stream,
-                unsigned long long* stamps = nullptr, const RowparDev* rowpar = nullptr) {
+                unsigned long long* stamps = nullptr, const RowparDev* rowpar = nullptr,
+                int rowpar_mode = HFRK_ROWPAR_AUTO) {
     int rc = validate(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype);
     if (rc != HFRK_SUCCESS) return rc;
     rc = prepare_device_once();
@@ -913,6 +971,15 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         memset(&p.rp, 0, sizeof(p.rp));
         if (rowpar != nullptr) {
             p.rp = *rowpar;
+            if (rowpar_mode == HFRK_ROWPAR_AUTO) {
+                // One-shot sends (world - 1) copies of this rank's fp32 partials; past about a
+                // megabyte the second NVLink crossing of the two-shot costs less than that traffic.
+                const unsigned long long one_shot_bytes =
+                    4ull * static_cast<unsigned long long>(mc) * n * static_cast<unsigned>(p.rp.world - 1);
+                p.rp.two_shot = one_shot_bytes >= kTwoShotFromBytes ? 1 : 0;
+            } else {
+                p.rp.two_shot = rowpar_mode == HFRK_ROWPAR_TWO_SHOT ? 1 : 0;
+            }
             const unsigned tiles = static_cast<unsigned>((n + kTileN - 1) / kTileN);
             if (static_cast<unsigned long long>(tiles) * mc * kTileN > p.rp.elems_per_src) return HFRK_TOO_LARGE;
         }
@@ -1100,6 +1167,7 @@ struct hfrk_rowpar {
     void* opened[hfrk::kMaxWorld] = {};   // peer mappings opened from IPC handles
     int device = 0;
     bool connected = false;
+    int mode = HFRK_ROWPAR_AUTO;
 };
 
 extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out) {
@@ -1112,7 +1180,8 @@ extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfr
     g->dev.rank = rank;
     g->dev.world = world;
     g->dev.elems_per_src = static_cast<unsigned>(tiles) * m_cap * hfrk::kTileN;
-    const size_t cells = (static_cast<size_t>(2) * world * g->dev.elems_per_src * sizeof(uint2) + 255) / 256 * 256;
+    const size_t cells =
+        (static_cast<size_t>(2) * (world + 1) * g->dev.elems_per_src * sizeof(uint2) + 255) / 256 * 256;
     g->block_bytes = cells + 256;
     cudaError_t err = cudaGetDevice(&g->device);
     if (err == cudaSuccess) err = cudaMalloc(&g->local_block, g->block_bytes);
@@ -1184,7 +1253,15 @@ extern "C" int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* g, const void* A, const 
     if (g == nullptr || !g->connected) return HFRK_BAD_WORLD;
     return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k_shard, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
                              HFRK_VARIANT_CLUSTER, 0, 0, 0, hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream),
-                             nullptr, &g->dev);
+                             nullptr, &g->dev, g->mode);
+}
+
+extern "C" int hfrk_rowpar_set_mode(hfrk_rowpar* g, int mode) {
+    if (g == nullptr) return HFRK_BAD_WORLD;
+    if (mode != HFRK_ROWPAR_AUTO && mode != HFRK_ROWPAR_ONE_SHOT && mode != HFRK_ROWPAR_TWO_SHOT)
+        return HFRK_INVALID_CONFIG;
+    g->mode = mode;
+    return HFRK_SUCCESS;
 }
 
 // =============================================================================== C ABI

@@ -17,6 +17,7 @@ E4M3FN, E4M3FNUZ = 0, 1
 F16, BF16, F32 = 0, 1, 2
 VARIANT_AUTO, VARIANT_CLUSTER, VARIANT_STREAMK = 0, 1, 2
 OUT_SAME, OUT_E4M3FN, OUT_E4M3FNUZ = 0, 1, 2
+ROWPAR_AUTO, ROWPAR_ONE_SHOT, ROWPAR_TWO_SHOT = 0, 1, 2
 
 STATUS_NAMES = {
     0: "SUCCESS", 1: "M_ABOVE_WARPTILE_M", 2: "N_NOT_EVEN", 3: "K_NOT_DIVISIBLE", 4: "TOO_MANY_WARPS",
@@ -32,7 +33,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect", "hfrk_rowpar_connect_pointers",
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
-    "hfrk_swiglu_fp8", "hfrk_residual_rms",
+    "hfrk_swiglu_fp8", "hfrk_residual_rms", "hfrk_rowpar_set_mode",
 )
 
 
@@ -62,6 +63,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_rowpar_local_block.argtypes = [vp]
     lib.hfrk_rowpar_local_block.restype = vp
     lib.hfrk_rowpar_destroy.argtypes = [vp]
+    lib.hfrk_rowpar_set_mode.argtypes = [vp, i32]
+    lib.hfrk_rowpar_set_mode.restype = i32
     lib.hfrk_skinny_gemm_fp8_rowpar.argtypes = [vp] + common + [vp]
     for name in ("hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect",
                  "hfrk_rowpar_connect_pointers", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar"):

@@ -27,7 +27,7 @@ class RowParallelSkinnyGemm:
     (unit inner stride; a column slice of the full weight works, its row pitch is kept). ``output``
     must hold the same values (zeros or the bias) on every rank and receives the full result on
     every rank. All ranks must make the same sequence of calls. ``max_m``/``max_n`` size the
-    exchange buffer (about ``2 * world * min(max_m, 16) * max_n * 4`` bytes per rank).
+    exchange buffer (``16 * (world + 1) * min(max_m, 16) * max_n`` bytes per rank).
     """
 
     def __init__(self, max_m: int, max_n: int, group: Optional[dist.ProcessGroup] = None,
@@ -63,6 +63,13 @@ class RowParallelSkinnyGemm:
                 m, n, k_shard, w_shard.stride(0), _capi.fp8_kind(a_shard.dtype), _capi.fp8_kind(w_shard.dtype),
                 _capi.out_kind(output.dtype), int(accumulate), stream_ptr))
         return output
+
+    def set_mode(self, mode: str = "auto") -> None:
+        """How partial tiles cross NVLink: "one_shot" (every rank sends to every peer), "two_shot"
+        (an owner rank per tile position adds up and sends the sums back) or "auto" (by traffic).
+        Every rank must choose the same."""
+        code = {"auto": _capi.ROWPAR_AUTO, "one_shot": _capi.ROWPAR_ONE_SHOT, "two_shot": _capi.ROWPAR_TWO_SHOT}[mode]
+        _capi.check(_capi.lib.hfrk_rowpar_set_mode(self._handle, code))
 
     def close(self) -> None:
         if getattr(self, "_handle", None) is not None:

@@ -138,6 +138,14 @@ int hfrk_rowpar_connect(hfrk_rowpar* group, const void* all_handles /* world x 6
 int hfrk_rowpar_connect_pointers(hfrk_rowpar* group, void* const* peer_blocks);
 void* hfrk_rowpar_local_block(hfrk_rowpar* group);
 int hfrk_rowpar_destroy(hfrk_rowpar* group);
+/* How the partial tiles cross NVLink. ONE_SHOT: every rank sends its fp32 partials to every peer
+ * and each adds them up itself (one crossing of latency, (world-1) copies of the partials out of
+ * every GPU). TWO_SHOT: each CTA position has an owner rank that receives the partials, adds them
+ * in rank order and sends the sums back (two crossings, about 2/world of the traffic). AUTO (the
+ * default) takes ONE_SHOT while the one-shot traffic per GPU, 4*m*n*(world-1) bytes, is below
+ * 1 MiB. Every rank of the group must use the same mode for the same call. */
+enum hfrk_rowpar_mode { HFRK_ROWPAR_AUTO = 0, HFRK_ROWPAR_ONE_SHOT = 1, HFRK_ROWPAR_TWO_SHOT = 2 };
+int hfrk_rowpar_set_mode(hfrk_rowpar* group, int mode);
 int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* group, const void* A_shard, const void* W_shard, void* D,
                                 const float* scale_dev, int m, int n, int k_shard, int64_t w_row_stride,
                                 int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);

@@ -21,6 +21,50 @@ from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl  # noqa: E402
 from hf_rocm_kernels.combined_ops import RowParallelSkinnyGemm, skinny_gemm_then_allreduce  # noqa: E402
 
 
+def tensor_parallel_mlp(group, dev, rank, world) -> None:
+    """llama_mlp_combined_ops with the gate/up weight split by columns and the down weight by rows
+    over the ranks, against the same block on one GPU with the whole weights. The partial sums are
+    added in another order than one GPU's K loop, so the results agree to the GEMM's tolerance, not
+    bit for bit; the ranks among themselves must agree bit for bit."""
+    from hf_rocm_kernels.combined_ops import llama_mlp_combined_ops
+    from hf_rocm_kernels.utils.fp8 import fp8_quantize_e4m3fn
+
+    tokens, hidden, inter = 16, 2048, 1024 * world
+    gen = torch.Generator().manual_seed(99)
+    attn = torch.randn(tokens, hidden, generator=gen).bfloat16().to(dev)
+    residual = torch.randn(tokens, hidden, generator=gen).bfloat16().to(dev)
+    rms_w = (1 + 0.1 * torch.randn(hidden, generator=gen)).bfloat16().to(dev)
+    q_gu, s_gu = fp8_quantize_e4m3fn((torch.randn(2 * inter, hidden, generator=gen) * 0.02).to(dev))
+    q_dn, s_dn = fp8_quantize_e4m3fn((torch.randn(hidden, inter, generator=gen) * 0.02).to(dev))
+    s_in = torch.tensor([4.0 / 448], device=dev)
+    s_act = torch.tensor([16.0 / 448], device=dev)
+
+    whole, whole_res = llama_mlp_combined_ops(attn, residual.clone(), rms_w, 1e-5, q_gu.t(), s_in, s_in * s_gu,
+                                              q_dn.t(), s_act, s_act * s_dn)
+    shard = inter // world
+    lo, hi = rank * shard, (rank + 1) * shard
+    gu_shard = torch.cat([q_gu.view(torch.uint8)[lo:hi], q_gu.view(torch.uint8)[inter + lo:inter + hi]])
+    gu_shard = gu_shard.view(torch.float8_e4m3fn)                       # [2 * shard, hidden]: gate_r then up_r
+    dn_shard = q_dn[:, lo:hi]                                           # [hidden, shard], row pitch of the whole
+    outs = []
+    for _ in range(2):
+        out, res = llama_mlp_combined_ops(attn, residual.clone(), rms_w, 1e-5, gu_shard.t(), s_in, s_in * s_gu,
+                                          dn_shard.t(), s_act, s_act * s_dn, down_row_parallel=group)
+        torch.cuda.synchronize()
+        outs.append(out)
+        assert torch.equal(res, whole_res)
+    assert _capi.device_status(clear=True)[0] == 0
+    assert torch.equal(outs[0], outs[1])
+    gathered = [torch.empty_like(outs[0]) for _ in range(world)]
+    dist.all_gather(gathered, outs[0])
+    assert all(torch.equal(g, outs[0]) for g in gathered), "ranks disagree on the MLP block"
+    diff = (outs[0].float() - whole.float()).abs()
+    # one bf16 step at the value, plus one at the block's typical magnitude for outputs that cancel to
+    # almost nothing (their float32 partial sums are added in a different order)
+    bound = whole.float().abs() * 2.0 ** -7 + whole.float().abs().mean() * 2.0 ** -7
+    assert bool((diff <= bound).all()), float((diff - bound).max())
+
+
 def main() -> None:
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -48,11 +92,15 @@ def main() -> None:
         floor = oracle.accumulation_floor(a_q, w_q, scale)
 
         outs = []
-        for _ in range(3):                           # epochs 1..3: both parities of the exchange buffer
+        # both exchange schemes (and the automatic choice), back to back on the same buffer; with
+        # three calls each, both parities of the buffer are reused under either scheme
+        for mode in ("one_shot", "one_shot", "two_shot", "two_shot", "two_shot", "one_shot", "auto"):
+            group.set_mode(mode)
             out = d0.clone()
             group(a_sh, w_sh, s, out)
             torch.cuda.synchronize()
             outs.append(out)
+        group.set_mode("auto")
         code, word = _capi.device_status(clear=True)
         assert code == 0, f"rank {rank}: device status {word:#x}"
         for out in outs:
@@ -93,6 +141,8 @@ def main() -> None:
     torch.cuda.synchronize()
     assert torch.equal(out, expect)
     assert _capi.device_status(clear=True)[0] == 0
+
+    tensor_parallel_mlp(group, dev, rank, world)
     dist.barrier()
     group.close()
     print("ROWPAR_OK", rank, flush=True)
