@@ -38,6 +38,7 @@
 #include "../../include/hfrk_b200.h"
 #include "host_common.h"
 #include "ptx_sm100.cuh"
+#include "elementwise_common.cuh"
 #include "skinny_gemm_common.cuh"
 #include "skinny_gemm_streamk.cuh"
 
@@ -85,6 +86,13 @@ struct GemmParams {
     int accumulate;
     unsigned long long* stamps;  // optional [cta][8] globaltimer samples (diagnostic entry point only)
     RowparDev rp;                // used by the row-parallel instantiation only
+    // used by the SwiGLU instantiation only: W holds act_cols gate rows followed by act_cols up rows
+    uint8_t* act_out;            // [m, act_cols] fp8
+    const float* act_scale;      // the activation is divided by this before the conversion to fp8
+    int act_cols;
+    int act_fnuz;                // 1 = write e4m3fnuz bytes, 0 = e4m3fn
+    uint8_t* zero_ptr;           // buffer the next GEMM accumulates into, zeroed by this grid
+    unsigned long long zero_bytes;
 };
 
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
@@ -234,9 +242,23 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
     return ok;
 }
 
-// kRowPar: the epilogue all-reduces the tile over the ranks of a row-parallel group before D is written.
-template <bool kRowPar>
-__global__ void __launch_bounds__(kThreads, kRowPar ? 2 : 1)
+// Instantiations of the kernel.
+//   kModePlain  : D <- D_in + scale * A.W^T
+//   kModeRowPar : the epilogue all-reduces the tile over the ranks of a row-parallel group before D is written
+//   kModeSwiglu : W is a gate/up projection; a CTA's tile is 64 gate rows plus the matching 64 up rows,
+//                 and the epilogue writes fp8(silu(gate) * up / act_scale) instead of the projection
+//                 (split == 1 and m <= 16 only: the host guarantees both)
+constexpr int kModePlain = 0;
+constexpr int kModeRowPar = 1;
+constexpr int kModeSwiglu = 2;
+constexpr int kHalfTile = kTileN / 2;
+
+__device__ __forceinline__ float round_trip_16(float x, int dtype) {
+    return dtype == HFRK_BF16 ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, kMode == kModeRowPar ? 2 : 1)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -256,10 +278,22 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int total = p.m * kTileN;
     const uint32_t chunk = ((static_cast<uint32_t>(total) + p.split - 1) / p.split + 3u) & ~3u;
 
+    constexpr bool kRowPar = kMode == kModeRowPar;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kTileN;
     if (threadIdx.x == 0) stamp(p, 0);
+    // One stage of W: a 128-row box, or (SwiGLU) the CTA's 64 gate rows and its 64 up rows, which
+    // land one after the other in the same 16 KiB and look like one 128-row tile to the MMA.
+    auto load_w = [&](uint32_t dst, uint32_t bar, int k_coord, uint64_t policy) {
+        if (kMode == kModeSwiglu) {
+            const int g0 = static_cast<int>(blockIdx.x) * kHalfTile;
+            tma_load_2d(dst, &tmap_w, bar, k_coord, g0, policy);
+            tma_load_2d(dst + kWStageBytes / 2, &tmap_w, bar, k_coord, p.act_cols + g0, policy);
+        } else {
+            tma_load_2d(dst, &tmap_w, bar, k_coord, n0, policy);
+        }
+    };
 
     // K blocks of this CTA: a contiguous range, the remainder spread over the first ranks.
     const int rank = p.split > 1 ? static_cast<int>(cluster_cta_rank()) : 0;
@@ -297,8 +331,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             // on the previous kernel, A does.
             for (int i = 0; i < prologue; ++i) {
                 mbar_arrive_expect_tx(full_bar + 8u * i, stage_bytes);
-                tma_load_2d(ring_addr + i * stage_bytes, &tmap_w, full_bar + 8u * i, (kb_start + i) * kBlockK, n0,
-                            pol_w);
+                load_w(ring_addr + i * stage_bytes, full_bar + 8u * i, (kb_start + i) * kBlockK, pol_w);
             }
             pdl_wait_prior_grids();
             for (int i = 0; i < prologue; ++i) {
@@ -333,8 +366,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const uint32_t round = static_cast<uint32_t>(i / p.stages);
                 if (!mbar_wait_bounded(empty_bar + 8u * s, (round - 1u) & 1u, &ctrl->abort, kRoleProducer)) break;
                 mbar_arrive_expect_tx(full_bar + 8u * s, stage_bytes);
-                tma_load_2d(ring_addr + s * stage_bytes, &tmap_w, full_bar + 8u * s, (kb_start + i) * kBlockK, n0,
-                            pol_w);
+                load_w(ring_addr + s * stage_bytes, full_bar + 8u * s, (kb_start + i) * kBlockK, pol_w);
                 tma_load_2d(ring_addr + s * stage_bytes + kWStageBytes, &tmap_a, full_bar + 8u * s,
                             (kb_start + i) * kBlockK, 0, pol_a);
                 issued = i + 1;
@@ -425,7 +457,66 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (threadIdx.x == 0) stamp(p, 5);
         tcgen05_fence_after_sync();
         float* const partial = reinterpret_cast<float*>(ring_ptr);  // the ring is idle by now
-        if (ok) {
+        if (kMode == kModeSwiglu) {
+            // Lanes 0..63 hold gate columns, lanes 64..127 the matching up columns. The projection is
+            // rounded to the 16-bit type first, as the unfused chain stores it, so both give the same
+            // bytes. The activation is shared out by tokens: the gate thread of a column takes tokens
+            // 0..7, the up thread tokens 8..15, and each hands the other the eight values it needs.
+            constexpr int kPitch = 9;                        // floats per column: no bank conflicts
+            float* const handed = partial;                   // [2][64][9]: up for tokens 0..7, gate for 8..15
+            uint8_t* const out_tile = reinterpret_cast<uint8_t*>(partial + 2 * kHalfTile * kPitch);  // [16][64]
+            const int col_in_tile = nl & (kHalfTile - 1);
+            const int half = nl >> 6;                        // 0: this lane holds gate values, 1: up values
+            float y[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) y[j] = 0.0f;
+            if (ok) {
+                uint32_t v[16];
+                tmem_ld_32x32b_x16(lane_taddr, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) y[j] = round_trip_16(__uint_as_float(v[j]) * scale, p.d_dtype);
+            }
+            {
+                // a gate lane gives away tokens 8..15, an up lane tokens 0..7
+                float* const dst = handed + ((1 - half) * kHalfTile + col_in_tile) * kPitch;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[j] = half == 0 ? y[8 + j] : y[j];
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+            {
+                const float inv_act = 1.0f / __ldg(p.act_scale);
+                const float* const src = handed + (half * kHalfTile + col_in_tile) * kPitch;
+                const int token0 = half * 8;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (token0 + j < p.m) {
+                        const float gate = half == 0 ? y[j] : src[j];
+                        const float up = half == 0 ? src[j] : y[8 + j];
+                        float t = (gate / (1.0f + expf(-gate))) * up * inv_act;
+                        if (p.act_fnuz) t *= 2.0f;
+                        uint8_t byte = static_cast<uint8_t>(pack_e4m3x2(t, 0.0f) & 0xffu);
+                        if (p.act_fnuz && byte == 0x80u) byte = 0;
+                        out_tile[(token0 + j) * kHalfTile + col_in_tile] = byte;
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+            if (nl < kHalfTile && ok) {
+                const int token = nl >> 2, piece = nl & 3;
+                const int col = static_cast<int>(blockIdx.x) * kHalfTile + piece * 16;
+                if (token < p.m && col < p.act_cols) {   // act_cols % 16 == 0: a piece is inside or outside
+                    *reinterpret_cast<uint4*>(p.act_out + static_cast<size_t>(token) * p.act_cols + col) =
+                        *reinterpret_cast<const uint4*>(out_tile + token * kHalfTile + piece * 16);
+                }
+            }
+            // the next GEMM adds into this buffer
+            const size_t vecs = static_cast<size_t>(p.zero_bytes / 16);
+            for (size_t i = static_cast<size_t>(blockIdx.x) * kEpilogueThreads + threadIdx.x; i < vecs;
+                 i += static_cast<size_t>(gridDim.x) * kEpilogueThreads) {
+                reinterpret_cast<uint4*>(p.zero_ptr)[i] = make_uint4(0, 0, 0, 0);
+            }
+        } else if (ok) {
             for (int c = 0; c < p.m_pad / 16; ++c) {
                 uint32_t v[16];
                 tmem_ld_32x32b_x16(lane_taddr + static_cast<uint32_t>(c * 16), v);
@@ -727,12 +818,16 @@ int prepare_device_once() {
     HFRK_CUDA_TRY(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && done[dev]) return HFRK_SUCCESS;
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSmemLimit));
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSmemLimit));
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModePlain>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModePlain>,
+                                       cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeRowPar>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeRowPar>,
+                                       cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeSwiglu>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<1>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<2>,
@@ -1007,14 +1102,90 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         cfg.attrs = attrs;
         cfg.numAttrs = num_attrs;
         if (rowpar != nullptr) {
-            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<true>, tmap_w, tmap_a, p));
+            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<kModeRowPar>, tmap_w, tmap_a, p));
         } else {
-            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<false>, tmap_w, tmap_a, p));
+            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<kModePlain>, tmap_w, tmap_a, p));
         }
     }
     return HFRK_SUCCESS;
 }
 
+// Gate/up projection with the SwiGLU, the fp8 quantisation of the down projection's input and the
+// zeroing of the down projection's accumulate buffer in the epilogue: one launch where the chain
+// has GEMM + swiglu. W is [2 * inter, k]: `inter` gate rows, then `inter` up rows. Tile t of the
+// grid takes gate rows [64t, 64t + 64) and up rows [inter + 64t, inter + 64t + 64), so that both
+// halves of every output column meet in one CTA. No K split: the epilogue needs whole sums.
+int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float* scale_dev,
+                       const float* act_scale_dev, void* next_buffer, int m, int inter, int k, int64_t w_row_stride,
+                       int a_kind, int w_kind, int mid_dtype, int out_kind, int64_t buffer_cols, int use_pdl,
+                       cudaStream_t stream) {
+    if (A == nullptr || W == nullptr || act_out == nullptr || scale_dev == nullptr || act_scale_dev == nullptr)
+        return HFRK_INVALID_CONFIG;
+    if (m <= 0 || inter <= 0 || k <= 0 || buffer_cols < 0) return HFRK_INVALID_CONFIG;
+    if (m > 16) return HFRK_TOO_LARGE;
+    if (inter % 16 != 0) return HFRK_INVALID_CONFIG;   // 16-byte pieces of the fp8 output rows
+    if ((a_kind != HFRK_E4M3FN && a_kind != HFRK_E4M3FNUZ) || (w_kind != HFRK_E4M3FN && w_kind != HFRK_E4M3FNUZ) ||
+        (mid_dtype != HFRK_F16 && mid_dtype != HFRK_BF16) || (out_kind != HFRK_E4M3FN && out_kind != HFRK_E4M3FNUZ))
+        return HFRK_BAD_DTYPE;
+    if (k % 16 != 0) return HFRK_K_NOT_DIVISIBLE;
+    const size_t zero_bytes = static_cast<size_t>(m) * static_cast<size_t>(buffer_cols) * 2;
+    if (zero_bytes != 0 && next_buffer == nullptr) return HFRK_INVALID_CONFIG;
+    if (w_row_stride < k || w_row_stride % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) ||
+        (reinterpret_cast<uintptr_t>(W) & 15u) || (reinterpret_cast<uintptr_t>(act_out) & 15u) ||
+        (reinterpret_cast<uintptr_t>(next_buffer) & 15u) || zero_bytes % 16 != 0)
+        return HFRK_BAD_ALIGNMENT;
+    int rc = prepare_device_once();
+    if (rc != HFRK_SUCCESS) return rc;
+
+    CUtensorMap tmap_w, tmap_a;
+    rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(2) * inter,
+                        static_cast<uint64_t>(w_row_stride), kHalfTile, &tmap_w);
+    if (rc != HFRK_SUCCESS) return rc;
+    Plan plan;
+    rc = make_plan(m, 2 * inter, k, /*split_req=*/1, /*stages_req=*/0, &plan);
+    if (rc != HFRK_SUCCESS) return rc;
+    rc = get_tensor_map(A, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                        static_cast<uint32_t>(plan.m_pad), &tmap_a);
+    if (rc != HFRK_SUCCESS) return rc;
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.scale = scale_dev;
+    p.kind_factor = (a_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f) * (w_kind == HFRK_E4M3FNUZ ? 0.5f : 1.0f);
+    p.m = m;
+    p.n = 2 * inter;
+    p.k = k;
+    p.m_pad = plan.m_pad;
+    p.num_kblocks = plan.num_kblocks;
+    p.split = 1;
+    p.stages = plan.stages;
+    p.d_dtype = mid_dtype;
+    p.accumulate = 0;
+    p.act_out = static_cast<uint8_t*>(act_out);
+    p.act_scale = act_scale_dev;
+    p.act_cols = inter;
+    p.act_fnuz = out_kind == HFRK_E4M3FNUZ ? 1 : 0;
+    p.zero_ptr = static_cast<uint8_t*>(next_buffer);
+    p.zero_bytes = zero_bytes;
+
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>((inter + kHalfTile - 1) / kHalfTile), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    unsigned num_attrs = 0;
+    if (use_pdl) {
+        attrs[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+        ++num_attrs;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = num_attrs;
+    HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<kModeSwiglu>, tmap_w, tmap_a, p));
+    return HFRK_SUCCESS;
+}
 
 }  // namespace
 }  // namespace hfrk
@@ -1276,6 +1447,15 @@ extern "C" int hfrk_skinny_gemm_fp8(const void* A, const void* W, void* D, const
                              static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int hfrk_skinny_gemm_fp8_swiglu(const void* A, const void* W_gate_up, void* act_out,
+                                           const float* scale_dev, const float* act_scale_dev, void* next_buffer,
+                                           int m, int inter, int k, int64_t w_row_stride, int a_kind, int w_kind,
+                                           int mid_dtype, int out_kind, int64_t buffer_cols, void* stream) {
+    return hfrk::launch_gemm_swiglu(A, W_gate_up, act_out, scale_dev, act_scale_dev, next_buffer, m, inter, k,
+                                    w_row_stride, a_kind, w_kind, mid_dtype, out_kind, buffer_cols,
+                                    hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* scale_dev, int m, int n,
                                        int k, int64_t w_row_stride, int a_kind, int w_kind, int d_dtype,
                                        int accumulate, int variant, int split_k, int ctas_per_sm, int num_stages,
@@ -1381,7 +1561,7 @@ extern "C" int hfrk_max_active_clusters(int split, int smem_bytes, int* clusters
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    HFRK_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, hfrk::skinny_gemm_fp8_sm100_kernel<false>, &cfg));
+    HFRK_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, hfrk::skinny_gemm_fp8_sm100_kernel<hfrk::kModePlain>, &cfg));
     *clusters_out = clusters;
     return HFRK_SUCCESS;
 }

@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
     "hfrk_swiglu_fp8", "hfrk_residual_rms", "hfrk_rowpar_set_mode",
+    "hfrk_skinny_gemm_fp8_swiglu",
 )
 
 
@@ -85,6 +86,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_swiglu_fp8.restype = i32
     lib.hfrk_residual_rms.argtypes = [vp, vp, vp, vp, ctypes.c_float, vp, vp, i32, i32, i64, i32, i32, i32, i32, vp]
     lib.hfrk_residual_rms.restype = i32
+    lib.hfrk_skinny_gemm_fp8_swiglu.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i32, i32, i32, i64, vp]
+    lib.hfrk_skinny_gemm_fp8_swiglu.restype = i32
     lib.hfrk_last_error.restype = ctypes.c_char_p
     for name in ("hfrk_skinny_gemm_fp8", "hfrk_skinny_gemm_fp8_ex", "hfrk_skinny_gemm_fp8_host",
                  "hfrk_skinny_gemm_fp8_simt", "hfrk_skinny_gemm_plan", "hfrk_device_status", "hfrk_version"):
@@ -199,6 +202,23 @@ def swiglu(gate_up: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, next_b
                                0 if next_buffer is None else next_buffer.data_ptr(), rows, two_hidden // 2,
                                buffer_cols, out_kind(gate_up.dtype), fp8_kind(out.dtype), int(force_scalar),
                                _stream_ptr(stream, gate_up.device))
+
+
+def skinny_gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, act_out: torch.Tensor, scale: torch.Tensor,
+                       act_scale: torch.Tensor, next_buffer: Optional[torch.Tensor] = None,
+                       mid_dtype: torch.dtype = torch.bfloat16, stream=None) -> int:
+    """hfrk_skinny_gemm_fp8_swiglu on torch tensors: a [m, k] fp8, w_gate_up [2*inter, k] fp8 with
+    unit inner stride, act_out [m, inter] fp8."""
+    m, k = a.shape
+    inter = w_gate_up.shape[0] // 2
+    assert w_gate_up.shape[1] == k and w_gate_up.stride(1) == 1 and a.is_contiguous() and act_out.is_contiguous()
+    assert tuple(act_out.shape) == (m, inter) and w_gate_up.shape[0] == 2 * inter
+    buffer_cols = 0 if next_buffer is None else next_buffer.numel() // m
+    return lib.hfrk_skinny_gemm_fp8_swiglu(
+        a.data_ptr(), w_gate_up.data_ptr(), act_out.data_ptr(), scale.data_ptr(), act_scale.data_ptr(),
+        0 if next_buffer is None else next_buffer.data_ptr(), m, inter, k, w_gate_up.stride(0), fp8_kind(a.dtype),
+        fp8_kind(w_gate_up.dtype), out_kind(mid_dtype), fp8_kind(act_out.dtype), buffer_cols,
+        _stream_ptr(stream, a.device))
 
 
 def residual_rms(input: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],

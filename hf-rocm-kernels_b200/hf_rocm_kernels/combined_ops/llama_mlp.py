@@ -18,8 +18,40 @@ from typing import Optional, Tuple
 import torch
 from torch import Tensor
 
-from hf_rocm_kernels import residual_rms, skinny_gemm, swiglu
+from hf_rocm_kernels import _capi, residual_rms, skinny_gemm, swiglu
 from hf_rocm_kernels.combined_ops.row_parallel import RowParallelSkinnyGemm
+
+
+def can_fuse_swiglu(tokens: int, hidden: int, intermediate: int) -> bool:
+    """True when the gate/up projection and swiglu can run as one launch: at most 16 tokens, output
+    rows that split into 16-byte pieces, and a gate/up matrix wide enough that the library would
+    not split K for it (the fused epilogue needs whole sums in one CTA)."""
+    if tokens > 16 or intermediate % 16 != 0:
+        return False
+    return _capi.plan(tokens, 2 * intermediate, hidden)["split_k"] == 1
+
+
+def skinny_gemm_swiglu(
+    skinny_a: Tensor,
+    gate_up_weight: Tensor,
+    scale_tensor: Tensor,
+    act_scale_tensor: Tensor,
+    next_buffer: Optional[Tensor] = None,
+    mid_dtype: torch.dtype = torch.bfloat16,
+    out_dtype: Optional[torch.dtype] = None,
+) -> Tensor:
+    """``fp8(silu(g) * u / act_scale)`` with ``[g | u] = round(scale * skinny_a @ gate_up_weight)``
+    in one launch: the same bytes as ``skinny_gemm`` into a ``mid_dtype`` buffer followed by
+    ``swiglu``. ``gate_up_weight`` is the (hidden, 2 * intermediate) column-major view, gate columns
+    first; ``next_buffer`` (16-bit, tokens rows) is zeroed."""
+    assert gate_up_weight.dim() == 2 and gate_up_weight.stride(0) == 1, "expected the column-major [K, N] view"
+    tokens, inter = skinny_a.size(0), gate_up_weight.size(1) // 2
+    out = torch.empty((tokens, inter), dtype=out_dtype or gate_up_weight.dtype, device=skinny_a.device)
+    status = _capi.skinny_gemm_swiglu(skinny_a, gate_up_weight.t(), out, scale_tensor, act_scale_tensor, next_buffer,
+                                      mid_dtype)
+    if status != 0:
+        raise RuntimeError(f"skinny_gemm_swiglu failed with status {status} ({_capi.STATUS_NAMES.get(status, '?')})")
+    return out
 
 
 def llama_mlp_combined_ops(
@@ -36,6 +68,7 @@ def llama_mlp_combined_ops(
     gate_up_gemm_hp: Tuple[Optional[int], Optional[int]] = (None, None),
     down_gemm_hp: Tuple[Optional[int], Optional[int]] = (None, None),
     down_row_parallel: Optional[RowParallelSkinnyGemm] = None,
+    fuse_swiglu: Optional[bool] = None,
 ) -> Tuple[Tensor, Tensor]:
     """Returns ``(mlp_output, residual)``; ``residual`` is updated in place to ``attn_output + residual``.
 
@@ -53,6 +86,8 @@ def llama_mlp_combined_ops(
         gate_up_gemm_hp, down_gemm_hp: (split_k, b_lanes) pairs of the reference's kernel;
             accepted so that existing callers keep working, not used (the library picks the
             launch shape per (m, n, k), or takes it from its tuning table)
+        fuse_swiglu: run the gate/up projection and swiglu as one launch (same bytes as the two
+            launches); ``None`` decides with :func:`can_fuse_swiglu`
         down_row_parallel: the exchange object of the ranks that share the block; every rank
             multiplies its slice of the swiglu output by its K shard of the down weight and all
             ranks receive the summed result (same bits on every rank)
@@ -61,22 +96,34 @@ def llama_mlp_combined_ops(
     tokens = attn_output.size(0)
     act_dtype = gate_up_weight.dtype
 
-    gate_up_proj = torch.empty((tokens, gate_up_weight.size(1)), dtype=attn_output.dtype, device=attn_output.device)
-    normalized, residual = residual_rms(
-        input=attn_output,
-        residual=residual,
-        weight=rms_weight,
-        epsilon=rms_epsilon,
-        scale_tensor=gate_up_input_scale,
-        next_buffer=gate_up_proj,
-        out_dtype=act_dtype,
-    )
-    skinny_gemm(skinny_a=normalized, b=gate_up_weight, scale_tensor=gate_up_output_scale, output=gate_up_proj)
-
+    hidden, inter = gate_up_weight.size(0), gate_up_weight.size(1) // 2
+    if fuse_swiglu is None:
+        fuse_swiglu = can_fuse_swiglu(tokens, hidden, inter)
     mlp_output = torch.empty((tokens, down_weight.size(1)), dtype=attn_output.dtype, device=attn_output.device)
-    swiglu_out = swiglu(
-        gate_up_proj=gate_up_proj, scale_tensor=down_input_scale, next_buffer=mlp_output, out_dtype=down_weight.dtype
-    )
+    if fuse_swiglu:
+        normalized, residual = residual_rms(
+            input=attn_output, residual=residual, weight=rms_weight, epsilon=rms_epsilon,
+            scale_tensor=gate_up_input_scale, next_buffer=None, out_dtype=act_dtype,
+        )
+        swiglu_out = skinny_gemm_swiglu(normalized, gate_up_weight, gate_up_output_scale, down_input_scale,
+                                        next_buffer=mlp_output, mid_dtype=attn_output.dtype,
+                                        out_dtype=down_weight.dtype)
+    else:
+        gate_up_proj = torch.empty((tokens, 2 * inter), dtype=attn_output.dtype, device=attn_output.device)
+        normalized, residual = residual_rms(
+            input=attn_output,
+            residual=residual,
+            weight=rms_weight,
+            epsilon=rms_epsilon,
+            scale_tensor=gate_up_input_scale,
+            next_buffer=gate_up_proj,
+            out_dtype=act_dtype,
+        )
+        skinny_gemm(skinny_a=normalized, b=gate_up_weight, scale_tensor=gate_up_output_scale, output=gate_up_proj)
+        swiglu_out = swiglu(
+            gate_up_proj=gate_up_proj, scale_tensor=down_input_scale, next_buffer=mlp_output,
+            out_dtype=down_weight.dtype,
+        )
     if down_row_parallel is None:
         skinny_gemm(skinny_a=swiglu_out, b=down_weight, scale_tensor=down_output_scale, output=mlp_output)
     else:

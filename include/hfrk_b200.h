@@ -233,6 +233,23 @@ int hfrk_residual_rms(const void* input, void* residual, const void* weight, con
                       int64_t buffer_cols, int dtype, int out_kind, int num_threads, int force_scalar,
                       void* stream);
 
+/* The gate/up projection of an MLP block with swiglu folded into its epilogue: one launch in
+ * place of hfrk_skinny_gemm_fp8 + hfrk_swiglu_fp8, with the same bytes as result.
+ *   act_out[m, inter] <- fp8( silu(g) * u / *act_scale_dev ),  next_buffer[m, buffer_cols] <- 0
+ *   where [g | u] = round16( *scale_dev * A[m, k] . W_gate_up[2*inter, k]^T )
+ * W_gate_up holds the `inter` gate rows followed by the `inter` up rows (the layout the unfused
+ * chain uses); a CTA's tile is 64 gate rows plus the matching 64 up rows. mid_dtype (HFRK_F16 or
+ * HFRK_BF16) is the type the unfused chain would have stored the projection in: the epilogue
+ * rounds to it before the activation so that fused and unfused results are identical bytes.
+ * Limits: m <= 16 (HFRK_TOO_LARGE), inter % 16 == 0, no bias, no K split (meant for gate/up
+ * matrices of at least ~148 tiles of 64 columns; narrower shards are faster unfused).
+ * act_out and next_buffer 16-byte aligned. No counterpart in the reference, whose
+ * combined_ops/llama_mlp.py:29-47 runs the two kernels one after the other. */
+int hfrk_skinny_gemm_fp8_swiglu(const void* A, const void* W_gate_up, void* act_out,
+                                const float* scale_dev, const float* act_scale_dev, void* next_buffer,
+                                int m, int inter, int k, int64_t w_row_stride, int a_kind, int w_kind,
+                                int mid_dtype, int out_kind, int64_t buffer_cols, void* stream);
+
 /* Pins the launch shape of (m, n, k) for every later automatic call in this process: split_k and
  * num_stages as in hfrk_skinny_gemm_fp8_ex (0 = leave that one to the built-in rule; both 0 = drop
  * the entry). Token counts share an entry per multiple of 16. Fed from the JSON the grid search

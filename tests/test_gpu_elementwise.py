@@ -303,6 +303,62 @@ def test_residual_rms_empty_and_invalid_inputs(capi, dev):
                                        torch.empty((2, 0), dtype=torch.float16, device=dev), 0, False)
 
 
+# ------------------------------------------------------- gate/up GEMM with swiglu in its epilogue
+@pytest.mark.parametrize("act_dtype,fp8_dtype", [(torch.float16, torch.float8_e4m3fnuz),
+                                                 (torch.bfloat16, torch.float8_e4m3fn)])
+@pytest.mark.parametrize("m,inter,k", [(16, 14336, 4096), (1, 14336, 4096), (5, 1040, 256), (16, 64, 128),
+                                       (3, 4144, 512), (9, 28672, 8192), (16, 16, 2048)])
+def test_fused_gemm_swiglu_writes_the_bytes_of_the_two_launches(capi, dev, m, inter, k, act_dtype, fp8_dtype):
+    """One launch (GEMM with the activation in its epilogue) against GEMM into a 16-bit buffer
+    followed by the swiglu kernel: identical bytes, zeroed buffer, nothing written out of bounds."""
+    from hf_rocm_kernels import skinny_gemm, swiglu
+    from hf_rocm_kernels.combined_ops import skinny_gemm_swiglu
+
+    torch.manual_seed(m * 7 + inter)
+    a = (torch.randn(m, k, device=dev) * 40).clamp(-200, 200).to(torch.float8_e4m3fn).view(torch.uint8)
+    w = (torch.randn(2 * inter, k, device=dev) * 40).clamp(-200, 200).to(torch.float8_e4m3fn).view(torch.uint8)
+    if fp8_dtype == torch.float8_e4m3fnuz:       # 0x80 is NaN there
+        a = torch.where(a == 0x80, torch.zeros_like(a), a)
+        w = torch.where(w == 0x80, torch.zeros_like(w), w)
+    a, w = a.view(fp8_dtype), w.view(fp8_dtype)
+    scale = torch.tensor([2.5 / (40.0 * 40.0 * k ** 0.5)], device=dev)
+    act_scale = torch.tensor([0.021], device=dev)
+
+    gate_up = torch.zeros((m, 2 * inter), dtype=act_dtype, device=dev)
+    skinny_gemm(a, w.t(), scale, gate_up)
+    buf_two = torch.full((m, 264), 3.0, dtype=act_dtype, device=dev)
+    expect = swiglu(gate_up, act_scale, buf_two, out_dtype=fp8_dtype)
+
+    buf_one = torch.full((m, 264), 3.0, dtype=act_dtype, device=dev)
+    got = skinny_gemm_swiglu(a, w.t(), scale, act_scale, buf_one, mid_dtype=act_dtype, out_dtype=fp8_dtype)
+    _device_ok(capi)
+    assert got.dtype == fp8_dtype and tuple(got.shape) == (m, inter)
+    assert torch.equal(got.view(torch.uint8), expect.view(torch.uint8))
+    assert int(torch.count_nonzero(buf_one)) == 0
+    spread = expect.view(torch.uint8).unique().numel()
+    assert spread > 8 or inter * m < 64, "degenerate test data"
+
+    # guard bytes either side of the output
+    backing = torch.full((m * inter + 64,), 0x55, dtype=torch.uint8, device=dev)
+    out = backing[32:32 + m * inter].view(m, inter).view(fp8_dtype)
+    capi.check(capi.skinny_gemm_swiglu(a, w, out, scale, act_scale, None, act_dtype))
+    _device_ok(capi)
+    assert torch.equal(out.view(torch.uint8), expect.view(torch.uint8))
+    guard = backing.cpu().numpy()
+    assert (guard[:32] == 0x55).all() and (guard[-32:] == 0x55).all()
+
+
+def test_fused_gemm_swiglu_rejects_what_it_cannot_do(capi, dev):
+    a = torch.zeros((17, 256), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    w = torch.zeros((256, 256), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    out = torch.empty((17, 128), dtype=torch.float8_e4m3fn, device=dev)
+    s = torch.ones(1, device=dev)
+    assert capi.skinny_gemm_swiglu(a, w, out, s, s) == 12                       # more than 16 tokens
+    w2 = torch.zeros((2 * 24, 256), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    assert capi.skinny_gemm_swiglu(a[:4], w2, out.flatten()[:4 * 24].view(4, 24), s, s) == 6   # inter % 16
+    assert capi.skinny_gemm_swiglu(a[:4], w, out[:4], s, s, mid_dtype=torch.float32) == 8
+
+
 # ------------------------------------------------------------------------------------ the MLP chain
 def _mlp_inputs(dev, tokens, hidden, inter, act_dtype, fp8_dtype):
     from hf_rocm_kernels.utils.fp8 import fp8_quantize, fp8_quantize_e4m3fn
@@ -346,6 +402,14 @@ def test_llama_mlp_chain_equals_its_parts_and_tracks_the_unquantised_block(capi,
 
     out, new_res = chain(p["residual"].clone())
     _device_ok(capi)
+    from hf_rocm_kernels.combined_ops import can_fuse_swiglu
+
+    assert can_fuse_swiglu(tokens, hidden, inter)          # so `chain` ran the three-launch form
+    for fuse in (False, True):
+        out_f, res_f = llama_mlp_combined_ops(p["attn"], p["residual"].clone(), p["rms_w"], 1e-5, p["q_gu"].t(),
+                                              p["in_scale_gu"], p["out_scale_gu"], p["q_dn"].t(), p["in_scale_dn"],
+                                              p["out_scale_dn"], fuse_swiglu=fuse)
+        assert torch.equal(out_f, out) and torch.equal(res_f, new_res)
 
     # step by step
     res2 = p["residual"].clone()
