@@ -59,6 +59,7 @@ class ClockSampler:
         self.mask = 0
         self.max_mhz = None
         self.stop_flag = threading.Event()
+        self.recording = threading.Event()
         self.thread = None
         self.error = None
 
@@ -87,11 +88,19 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._poll, daemon=True)
         self.thread.start()
 
+    def begin(self):
+        """Samples taken from here on count: the thread is started earlier so that the first,
+        slow NVML queries fall outside the timed region."""
+        self.recording.set()
+
     def _poll(self):
         while not self.stop_flag.is_set():
             try:
-                self.sm.append(float(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)))
-                self.mask |= int(self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                mhz = float(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+                reasons = int(self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                if self.recording.is_set():
+                    self.sm.append(mhz)
+                    self.mask |= reasons
             except Exception as exc:
                 self.error = repr(exc)[:120]
                 return
@@ -208,13 +217,14 @@ def run_ours(args):
         with torch.cuda.graph(graph, stream=stream):
             for it in items:
                 hf_rocm_kernels.skinny_gemm(it["a"], it["w"].t(), it["scale"], it["d"])
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
         for _ in range(max(args.warmup, 3)):
             graph.replay()
         stream.synchronize()
         barrier()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
+        sampler.begin()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):

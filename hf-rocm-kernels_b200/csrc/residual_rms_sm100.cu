@@ -217,8 +217,13 @@ residual_rms_scalar_kernel(const T* __restrict__ input, T* __restrict__ residual
     zero_range(next_buffer, buffer_bytes);
 }
 
-int choose_threads(int work_items, int hint) {
+// CTA size. A hint that is a multiple of 32 is taken as it is. Otherwise one work item (a 16-byte
+// vector, or an element on the scalar path) per thread: the shortest critical path, which is what
+// the few rows of a decode step need. With more rows than the machine holds CTAs at once, two items
+// per thread: smaller CTAs, more of them per SM, so one CTA's reduction overlaps another's loads.
+int choose_threads(int work_items, int rows, int hint) {
     if (hint >= 32 && hint <= 1024 && hint % 32 == 0) return hint;
+    if (rows > 2 * kSmCount) work_items = (work_items + 1) / 2;
     int threads = ((work_items + 31) / 32) * 32;
     if (threads < 64) threads = 64;
     if (threads > 1024) threads = 1024;
@@ -235,11 +240,11 @@ int launch_residual_rms(const void* input, void* residual, const void* weight, c
     uint8_t* nb = static_cast<uint8_t*>(next_buffer);
     const unsigned grid = static_cast<unsigned>(rows);
     if (vec) {
-        const unsigned block = static_cast<unsigned>(choose_threads(cols / 8, num_threads));
+        const unsigned block = static_cast<unsigned>(choose_threads(cols / 8, rows, num_threads));
         return launch_elementwise(residual_rms_vec8_kernel<T, kOut>, grid, block, stream, in, res, w, scale_dev,
                                   epsilon, output, nb, buffer_bytes, cols);
     }
-    const unsigned block = static_cast<unsigned>(choose_threads(cols, num_threads));
+    const unsigned block = static_cast<unsigned>(choose_threads(cols, rows, num_threads));
     return launch_elementwise(residual_rms_scalar_kernel<T, kOut>, grid, block, stream, in, res, w, scale_dev,
                               epsilon, output, nb, buffer_bytes, cols);
 }
