@@ -1481,10 +1481,35 @@ extern "C" int64_t hfrk_host_call_workspace_bytes(int m, int n, int k) {
     return a_bytes + d_bytes;
 }
 
+namespace hfrk {
+namespace {
+int host_call(const void* A_host, const void* W_dev, void* D_host, const float* scale_dev, int m, int n, int k,
+              int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, void* work_dev, void* stream,
+              bool synchronise);
+}  // namespace
+}  // namespace hfrk
+
 extern "C" int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, void* D_host,
                                          const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
                                          int a_kind, int w_kind, int d_dtype, int accumulate, void* work_dev,
                                          void* stream) {
+    return hfrk::host_call(A_host, W_dev, D_host, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype,
+                           accumulate, work_dev, stream, true);
+}
+
+extern "C" int hfrk_skinny_gemm_fp8_host_async(const void* A_host, const void* W_dev, void* D_host,
+                                               const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
+                                               int a_kind, int w_kind, int d_dtype, int accumulate, void* work_dev,
+                                               void* stream) {
+    return hfrk::host_call(A_host, W_dev, D_host, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype,
+                           accumulate, work_dev, stream, false);
+}
+
+namespace hfrk {
+namespace {
+int host_call(const void* A_host, const void* W_dev, void* D_host, const float* scale_dev, int m, int n, int k,
+              int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, void* work_dev, void* stream,
+              bool synchronise) {
     if (A_host == nullptr || D_host == nullptr || work_dev == nullptr || m <= 0 || n <= 0 || k <= 0)
         return HFRK_INVALID_CONFIG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1498,9 +1523,11 @@ extern "C" int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, 
                                accumulate, HFRK_VARIANT_AUTO, 0, 0, 0, hfrk::default_use_pdl(), s);
     if (rc != HFRK_SUCCESS) return rc;
     HFRK_CUDA_TRY(cudaMemcpyAsync(D_host, d_dev, d_bytes, cudaMemcpyDeviceToHost, s));
-    HFRK_CUDA_TRY(cudaStreamSynchronize(s));
+    if (synchronise) HFRK_CUDA_TRY(cudaStreamSynchronize(s));
     return HFRK_SUCCESS;
 }
+}  // namespace
+}  // namespace hfrk
 
 extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8) {
     if (out8 == nullptr || variant < HFRK_VARIANT_AUTO || variant > HFRK_VARIANT_STREAMK) return HFRK_INVALID_CONFIG;

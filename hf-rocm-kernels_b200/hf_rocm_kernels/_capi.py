@@ -34,7 +34,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_rowpar_local_block", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar",
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
     "hfrk_swiglu_fp8", "hfrk_residual_rms", "hfrk_rowpar_set_mode",
-    "hfrk_skinny_gemm_fp8_swiglu",
+    "hfrk_skinny_gemm_fp8_swiglu", "hfrk_skinny_gemm_fp8_host_async",
 )
 
 
@@ -55,6 +55,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_skinny_gemm_fp8.argtypes = common + [i32, vp]
     lib.hfrk_skinny_gemm_fp8_ex.argtypes = common + [i32, i32, i32, i32, i32, vp]
     lib.hfrk_skinny_gemm_fp8_host.argtypes = common + [vp, vp]
+    lib.hfrk_skinny_gemm_fp8_host_async.argtypes = common + [vp, vp]
+    lib.hfrk_skinny_gemm_fp8_host_async.restype = i32
     lib.hfrk_skinny_gemm_fp8_profile.argtypes = common + [i32, i32, i32, i32, i32, vp, vp]
     lib.hfrk_skinny_gemm_fp8_profile.restype = i32
     lib.hfrk_rowpar_create.argtypes = [i32, i32, i32, i32, ctypes.POINTER(vp)]
@@ -179,14 +181,18 @@ def skinny_gemm_noalloc(a, w, d, scale, accumulate=True, stream=None) -> int:
                                                 _stream_ptr(stream, a.device))
 
 
-def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True, stream=None) -> int:
-    """Host-buffer call: ``a_host``/``d_host`` are (pinned) CPU tensors, weights and scale stay on the GPU."""
+def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True, stream=None,
+                     synchronise=True) -> int:
+    """Host-buffer call: ``a_host``/``d_host`` are (pinned) CPU tensors, weights and scale stay on the
+    GPU. With ``synchronise=False`` the copies and the GEMM are only queued on the stream
+    (hfrk_skinny_gemm_fp8_host_async): ``d_host`` is valid after the caller synchronises it."""
     m, k = a_host.shape
     n = w_dev.shape[0]
     assert a_host.device.type == "cpu" and d_host.device.type == "cpu" and w_dev.stride(1) == 1
     assert work_dev.numel() * work_dev.element_size() >= lib.hfrk_host_call_workspace_bytes(m, n, k)
+    entry = lib.hfrk_skinny_gemm_fp8_host if synchronise else lib.hfrk_skinny_gemm_fp8_host_async
     with torch.cuda.device(w_dev.device):
-        return lib.hfrk_skinny_gemm_fp8_host(
+        return entry(
             a_host.data_ptr(), w_dev.data_ptr(), d_host.data_ptr(), scale_dev.data_ptr(), m, n, k, w_dev.stride(0),
             fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype), out_kind(d_host.dtype), int(accumulate),
             work_dev.data_ptr(), _stream_ptr(stream, w_dev.device))

@@ -112,6 +112,14 @@ int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, void* D_hos
                               int a_kind, int w_kind, int d_dtype, int accumulate,
                               void* work_dev, void* stream);
 int64_t hfrk_host_call_workspace_bytes(int m, int n, int k);
+/* The same three copies and the GEMM queued on `stream` WITHOUT the final synchronisation: D_host
+ * holds the result once the caller has synchronised the stream. A_host, D_host (pinned, or the
+ * copies are not asynchronous) and work_dev must stay untouched until then; calls that share a
+ * work_dev must share the stream. Lets a decode step queue all of its projections and wait once. */
+int hfrk_skinny_gemm_fp8_host_async(const void* A_host, const void* W_dev, void* D_host,
+                                    const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
+                                    int a_kind, int w_kind, int d_dtype, int accumulate,
+                                    void* work_dev, void* stream);
 
 /* ---- row-parallel (K split over GPUs) GEMM with the all-reduce fused into its epilogue ---------
  * Rank r of `world` holds columns [r*K/world, (r+1)*K/world) of A and W. Every rank calls

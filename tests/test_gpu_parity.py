@@ -294,6 +294,16 @@ def test_host_buffer_entry_point(capi, dev, checker):
     capi.check(capi.skinny_gemm_host(a_host, w, d_host, s, work))    # synchronous
     checker(d_host, inp["a"], inp["w"], float(inp["scale"][0]), inp["d_in"], "host_call")
 
+    # the queued form: several calls on two streams, one wait at the end, the same bytes
+    lanes = [(torch.cuda.Stream(dev), torch.empty_like(work)) for _ in range(2)]
+    outs = [inp["d_in"].clone().pin_memory() for _ in range(6)]
+    for i, out in enumerate(outs):
+        stream, lane_work = lanes[i % 2]
+        capi.check(capi.skinny_gemm_host(a_host, w, out, s, lane_work, stream=stream, synchronise=False))
+    for stream, _ in lanes:
+        stream.synchronize()
+    assert all(torch.equal(out, d_host) for out in outs)
+
 
 def test_profile_entry_point_records_ordered_stamps(capi, dev):
     a = torch.randint(0, 120, (16, 4096), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
