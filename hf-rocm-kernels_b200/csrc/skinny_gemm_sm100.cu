@@ -79,6 +79,7 @@ struct GemmParams {
     float kind_factor;   // 0.5 per e4m3fnuz operand
     int m, n, k;
     int m_pad;           // MMA N: m rounded up to 16
+    int tile_rows;       // W rows per CTA, <= 128: the MMA always covers 128 lanes, the rest is ignored
     int num_kblocks;     // ceil(k / 128)
     int split;           // CTAs per cluster along K
     int stages;
@@ -252,6 +253,7 @@ constexpr int kModePlain = 0;
 constexpr int kModeRowPar = 1;
 constexpr int kModeSwiglu = 2;
 constexpr int kHalfTile = kTileN / 2;
+constexpr int kAutoTileRowsOff = -1;   // make_plan: keep 128-row tiles (callers whose layout depends on them)
 
 __device__ __forceinline__ float round_trip_16(float x, int dtype) {
     return dtype == HFRK_BF16 ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
@@ -268,6 +270,9 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     uint8_t* const ring_ptr = smem_raw + (ring_addr - raw_addr);
     const uint32_t a_bytes = static_cast<uint32_t>(p.m_pad) * kBlockK;
     const uint32_t stage_bytes = kWStageBytes + a_bytes;
+    // Bytes that land per stage: a W box of tile_rows rows (rows beyond it keep stale shared memory;
+    // their accumulator lanes are never stored) and the activations.
+    const uint32_t stage_tx = static_cast<uint32_t>(p.tile_rows) * kBlockK + a_bytes;
     Ctrl* const ctrl = reinterpret_cast<Ctrl*>(ring_ptr + static_cast<size_t>(p.stages) * stage_bytes);
     const uint32_t full_bar = smem_u32(&ctrl->full[0]);
     const uint32_t empty_bar = smem_u32(&ctrl->empty[0]);
@@ -281,7 +286,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     constexpr bool kRowPar = kMode == kModeRowPar;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTileN;
+    const int n0 = blockIdx.x * p.tile_rows;
     if (threadIdx.x == 0) stamp(p, 0);
     // One stage of W: a 128-row box, or (SwiGLU) the CTA's 64 gate rows and its 64 up rows, which
     // land one after the other in the same 16 KiB and look like one 128-row tile to the MMA.
@@ -330,7 +335,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             // Start the weight stream before anything else in the CTA is ready: W does not depend
             // on the previous kernel, A does.
             for (int i = 0; i < prologue; ++i) {
-                mbar_arrive_expect_tx(full_bar + 8u * i, stage_bytes);
+                mbar_arrive_expect_tx(full_bar + 8u * i, stage_tx);
                 load_w(ring_addr + i * stage_bytes, full_bar + 8u * i, (kb_start + i) * kBlockK, pol_w);
             }
             pdl_wait_prior_grids();
@@ -365,7 +370,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 const int s = i % p.stages;
                 const uint32_t round = static_cast<uint32_t>(i / p.stages);
                 if (!mbar_wait_bounded(empty_bar + 8u * s, (round - 1u) & 1u, &ctrl->abort, kRoleProducer)) break;
-                mbar_arrive_expect_tx(full_bar + 8u * s, stage_bytes);
+                mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
                 load_w(ring_addr + s * stage_bytes, full_bar + 8u * s, (kb_start + i) * kBlockK, pol_w);
                 tma_load_2d(ring_addr + s * stage_bytes + kWStageBytes, &tmap_a, full_bar + 8u * s,
                             (kb_start + i) * kBlockK, 0, pol_a);
@@ -424,6 +429,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         pdl_wait_prior_grids();
         const int nl = threadIdx.x;  // TMEM lane = W row inside the tile
         const int n = n0 + nl;
+        const bool lane_valid = nl < p.tile_rows && n < p.n;
         const bool direct = p.split == 1;
         const float scale = __ldg(p.scale) * p.kind_factor;
         const uint32_t lane_taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
@@ -436,7 +442,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         float din[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            din[j] = (direct && p.accumulate && j < p.m && n < p.n)
+            din[j] = (direct && p.accumulate && j < p.m && lane_valid)
                          ? load_out(p.d, static_cast<size_t>(j) * p.n + n, p.d_dtype)
                          : 0.0f;
         }
@@ -446,7 +452,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const uint32_t off = threadIdx.x + it * kEpilogueThreads;
             const int e = static_cast<int>(rank * chunk + off);
             const int col = n0 + (e % kTileN);
-            d_own[it] = (!direct && p.accumulate && off < chunk && e < total && col < p.n)
+            d_own[it] = (!direct && p.accumulate && off < chunk && e < total && (e % kTileN) < p.tile_rows && col < p.n)
                             ? load_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype)
                             : 0.0f;
         }
@@ -538,7 +544,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = c * 16 + j;
-                        if (ok && m < p.m && n < p.n) {
+                        if (ok && m < p.m && lane_valid) {
                             const size_t idx = static_cast<size_t>(m) * p.n + n;
                             const float d_in = c == 0 ? din[j] : (p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f);
                             store_out(p.d, idx, p.d_dtype, fmaf(__uint_as_float(v[j]), scale, d_in));
@@ -591,7 +597,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     const int e = static_cast<int>(rank * chunk + off);
                     if (landed && off < chunk && e < total) {
                         const int col = n0 + (e % kTileN);
-                        if (col < p.n) {
+                        if ((e % kTileN) < p.tile_rows && col < p.n) {
                             store_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype,
                                       fmaf(own[it], scale, d_own[it]));
                         }
@@ -604,7 +610,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     float sum = 0.0f;
                     for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + off];
                     const int col = n0 + (e % kTileN);
-                    if (col < p.n) {
+                    if ((e % kTileN) < p.tile_rows && col < p.n) {
                         const size_t idx = static_cast<size_t>(e / kTileN) * p.n + col;
                         const float d0 = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
                         store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d0));
@@ -720,7 +726,7 @@ int get_tensor_map(const void* base, uint64_t inner, uint64_t outer, uint64_t st
 }
 
 struct Plan {
-    int split, stages, ctas, smem_bytes, m_pad, num_kblocks;
+    int split, stages, ctas, smem_bytes, m_pad, num_kblocks, tile_rows, tiles;
 };
 
 int round_up(int v, int to) { return (v + to - 1) / to * to; }
@@ -739,7 +745,7 @@ struct TuneKeyHash {
     }
 };
 struct TuneValue {
-    int split, stages;
+    int split, stages, tile_rows;
 };
 std::mutex g_tune_mutex;
 std::unordered_map<TuneKey, TuneValue, TuneKeyHash> g_tune_table;
@@ -763,8 +769,17 @@ bool tuning_lookup(int m_pad, int n, int k, TuneValue* out) {
 //     The split is the largest one with tiles * split <= 280 and at least two K blocks per CTA,
 //     capped at 8 (12 below 25 tiles, 16 below 11: very narrow shards need it to reach the SMs);
 //   * without a split (tiles alone cover the SMs) a ring of six stages, two CTAs per SM.
-int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
+//   * tiles of fewer than 128 rows can even out a grid without a K split that is between one and
+//     two CTAs per SM: 224 tiles of 128 rows put two CTAs on 76 SMs and one on the other 72, and
+//     the grid ends when the doubly loaded SMs are done; 279 tiles of 103 rows load nearly every
+//     SM twice. The tensor core still computes 128 lanes per tile (it idles at a few per cent
+//     anyway); the lanes past the tile's rows are ignored. Measured gain on 28672 x 4096: 2.4 %.
+//     Nowhere else: with clusters a taller grid crosses the residency cliff (35 clusters of 8
+//     instead of 32: +45 % time), and grids of several waves got slower (57344 x 8192: +2 %).
+int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan, int tile_rows_req = 0) {
     if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
+    if (tile_rows_req < kAutoTileRowsOff || tile_rows_req > kTileN || (tile_rows_req > 0 && tile_rows_req < 8))
+        return HFRK_INVALID_CONFIG;
     if (split_req < 0 || split_req > kMaxSplit || stages_req < 0 || stages_req == 1 || stages_req > kMaxStages)
         return HFRK_INVALID_CONFIG;
     const int m_pad = round_up(m, 16);
@@ -774,9 +789,10 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     constexpr int kResidentTarget = 280;
 
     TuneValue tuned;
-    if (split_req == 0 && stages_req == 0 && tuning_lookup(m_pad, n, k, &tuned)) {
+    if (split_req == 0 && stages_req == 0 && tile_rows_req == 0 && tuning_lookup(m_pad, n, k, &tuned)) {
         split_req = tuned.split;
         stages_req = tuned.stages;
+        tile_rows_req = tuned.tile_rows;
     }
     int split = split_req;
     if (split == 0) {
@@ -802,9 +818,23 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan) {
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return HFRK_INVALID_CONFIG;
 
+    int tile_rows = tile_rows_req == kAutoTileRowsOff ? kTileN : tile_rows_req;
+    if (tile_rows == 0) {
+        tile_rows = kTileN;
+        const int smem = fixed_bytes + stages * stage_bytes;
+        if (m_pad == 16 && split == 1 && tiles > kNumSms && tiles <= kResidentTarget &&
+            2 * (smem + 1024) <= 228 * 1024) {
+            const int rows = (n + kResidentTarget - 1) / kResidentTarget;
+            if (rows >= 64 && rows < tile_rows) tile_rows = rows;
+        }
+    }
+    const int tiles_used = (n + tile_rows - 1) / tile_rows;
+
     plan->split = split;
     plan->stages = stages;
-    plan->ctas = tiles * split;
+    plan->tile_rows = tile_rows;
+    plan->tiles = tiles_used;
+    plan->ctas = tiles_used * split;
     plan->smem_bytes = fixed_bytes + stages * stage_bytes;
     plan->m_pad = m_pad;
     plan->num_kblocks = nkb;
@@ -1017,7 +1047,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
                 int64_t w_row_stride, int a_kind, int w_kind, int d_dtype, int accumulate, int variant,
                 int split_req, int ctas_per_sm, int stages_req, int use_pdl, cudaStream_t stream,
                 unsigned long long* stamps = nullptr, const RowparDev* rowpar = nullptr,
-                int rowpar_mode = HFRK_ROWPAR_AUTO) {
+                int rowpar_mode = HFRK_ROWPAR_AUTO, int tile_rows_req = 0) {
     int rc = validate(A, W, D, scale_dev, m, n, k, w_row_stride, a_kind, w_kind, d_dtype);
     if (rc != HFRK_SUCCESS) return rc;
     rc = prepare_device_once();
@@ -1030,18 +1060,18 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
                               ctas_per_sm, stages_req, use_pdl, stream, stamps);
     }
 
-    CUtensorMap tmap_w;
-    rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(w_row_stride),
-                        kTileN, &tmap_w);
-    if (rc != HFRK_SUCCESS) return rc;
-
     const size_t out_elem = d_dtype == HFRK_F32 ? 4 : 2;
     // the fused all-reduce keeps a thread's share of the tile in registers: 16 tokens per launch
     const int m_step = rowpar != nullptr ? 16 : kMaxMPad;
     for (int m0 = 0; m0 < m; m0 += m_step) {
         const int mc = m - m0 < m_step ? m - m0 : m_step;
         Plan plan;
-        rc = make_plan(mc, n, k, split_req, stages_req, &plan);
+        // the exchange buffer of the row-parallel kernel is laid out in 128-row tiles
+        rc = make_plan(mc, n, k, split_req, stages_req, &plan, rowpar != nullptr ? kAutoTileRowsOff : tile_rows_req);
+        if (rc != HFRK_SUCCESS) return rc;
+        CUtensorMap tmap_w;
+        rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                            static_cast<uint64_t>(w_row_stride), static_cast<uint32_t>(plan.tile_rows), &tmap_w);
         if (rc != HFRK_SUCCESS) return rc;
         const uint8_t* a_chunk = static_cast<const uint8_t*>(A) + static_cast<size_t>(m0) * k;
         CUtensorMap tmap_a;
@@ -1057,6 +1087,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         p.n = n;
         p.k = k;
         p.m_pad = plan.m_pad;
+        p.tile_rows = plan.tile_rows;
         p.num_kblocks = plan.num_kblocks;
         p.split = plan.split;
         p.stages = plan.stages;
@@ -1081,7 +1112,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
 
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
-        cfg.gridDim = dim3(static_cast<unsigned>((n + kTileN - 1) / kTileN), static_cast<unsigned>(plan.split), 1);
+        cfg.gridDim = dim3(static_cast<unsigned>(plan.tiles), static_cast<unsigned>(plan.split), 1);
         cfg.blockDim = dim3(kThreads, 1, 1);
         cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
         cfg.stream = stream;
@@ -1142,7 +1173,7 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
                         static_cast<uint64_t>(w_row_stride), kHalfTile, &tmap_w);
     if (rc != HFRK_SUCCESS) return rc;
     Plan plan;
-    rc = make_plan(m, 2 * inter, k, /*split_req=*/1, /*stages_req=*/0, &plan);
+    rc = make_plan(m, 2 * inter, k, /*split_req=*/1, /*stages_req=*/0, &plan, kAutoTileRowsOff);
     if (rc != HFRK_SUCCESS) return rc;
     rc = get_tensor_map(A, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                         static_cast<uint32_t>(plan.m_pad), &tmap_a);
@@ -1156,6 +1187,7 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
     p.n = 2 * inter;
     p.k = k;
     p.m_pad = plan.m_pad;
+    p.tile_rows = kTileN;
     p.num_kblocks = plan.num_kblocks;
     p.split = 1;
     p.stages = plan.stages;
@@ -1539,7 +1571,7 @@ extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split
         if (rc != HFRK_SUCCESS) return rc;
         out8[0] = variant; out8[1] = plan.split; out8[2] = plan.stages; out8[3] = plan.ctas;
         out8[4] = plan.smem_bytes; out8[5] = plan.m_pad; out8[6] = plan.num_kblocks;
-        out8[7] = (n + hfrk::kTileN - 1) / hfrk::kTileN;
+        out8[7] = plan.tiles;
         return HFRK_SUCCESS;
     }
     hfrk::SkPlan plan;
@@ -1550,18 +1582,22 @@ extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split
     return HFRK_SUCCESS;
 }
 
-extern "C" int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages) {
+extern "C" int hfrk_tuning_set_ex(int m, int n, int k, int split_k, int num_stages, int tile_rows) {
     if (m <= 0 || n <= 0 || k <= 0 || split_k < 0 || split_k > hfrk::kMaxSplit || num_stages < 0 || num_stages == 1 ||
-        num_stages > hfrk::kMaxStages)
+        num_stages > hfrk::kMaxStages || tile_rows < 0 || tile_rows > hfrk::kTileN || (tile_rows > 0 && tile_rows < 8))
         return HFRK_INVALID_CONFIG;
     const int m_pad = hfrk::round_up(m > hfrk::kMaxMPad ? hfrk::kMaxMPad : m, 16);
     std::lock_guard<std::mutex> lock(hfrk::g_tune_mutex);
-    if (split_k == 0 && num_stages == 0) {
+    if (split_k == 0 && num_stages == 0 && tile_rows == 0) {
         hfrk::g_tune_table.erase(hfrk::TuneKey{m_pad, n, k});
     } else {
-        hfrk::g_tune_table[hfrk::TuneKey{m_pad, n, k}] = hfrk::TuneValue{split_k, num_stages};
+        hfrk::g_tune_table[hfrk::TuneKey{m_pad, n, k}] = hfrk::TuneValue{split_k, num_stages, tile_rows};
     }
     return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages) {
+    return hfrk_tuning_set_ex(m, n, k, split_k, num_stages, 0);
 }
 
 extern "C" int hfrk_tuning_clear(void) {

@@ -35,6 +35,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
     "hfrk_swiglu_fp8", "hfrk_residual_rms", "hfrk_rowpar_set_mode",
     "hfrk_skinny_gemm_fp8_swiglu", "hfrk_skinny_gemm_fp8_host_async",
+    "hfrk_tuning_set_ex",
 )
 
 
@@ -83,6 +84,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_max_active_clusters.restype = i32
     lib.hfrk_tuning_set.argtypes = [i32, i32, i32, i32, i32]
     lib.hfrk_tuning_set.restype = i32
+    lib.hfrk_tuning_set_ex.argtypes = [i32, i32, i32, i32, i32, i32]
+    lib.hfrk_tuning_set_ex.restype = i32
     lib.hfrk_tuning_clear.restype = i32
     lib.hfrk_swiglu_fp8.argtypes = [vp, vp, vp, vp, i32, i32, i64, i32, i32, i32, vp]
     lib.hfrk_swiglu_fp8.restype = i32

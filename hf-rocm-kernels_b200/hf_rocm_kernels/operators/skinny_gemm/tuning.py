@@ -7,7 +7,8 @@ loads it into the library, which consults it before its built-in rule. B200 chip
 their SMs are spread over the GPCs, and with it the largest cluster shape that is resident at
 once, so a table measured on the deployment's own GPUs can beat the rule by a few percent.
 
-File format: ``{"entries": [{"m": 16, "n": 4096, "k": 4096, "split_k": 8, "num_stages": 4}, ...]}``.
+File format: ``{"entries": [{"m": 16, "n": 4096, "k": 4096, "split_k": 8, "num_stages": 4}, ...]}``;
+an entry may also carry ``"tile_rows"`` (W rows per CTA, 8..128; absent or 0 = the built-in rule).
 Set ``HFRK_TUNING_FILE`` to have it loaded when the operator is imported.
 """
 import json
@@ -21,8 +22,8 @@ def apply_tuning(entries: Iterable[Dict[str, int]]) -> int:
     """Pins every entry; returns how many were accepted."""
     accepted = 0
     for e in entries:
-        code = _capi.lib.hfrk_tuning_set(int(e["m"]), int(e["n"]), int(e["k"]), int(e.get("split_k", 0)),
-                                         int(e.get("num_stages", 0)))
+        code = _capi.lib.hfrk_tuning_set_ex(int(e["m"]), int(e["n"]), int(e["k"]), int(e.get("split_k", 0)),
+                                            int(e.get("num_stages", 0)), int(e.get("tile_rows", 0)))
         accepted += int(code == 0)
     return accepted
 

@@ -196,7 +196,7 @@ int hfrk_skinny_gemm_fp8_profile(const void* A, const void* W, void* D, const fl
 /* Launch shape for (m, n, k) and the given pins (for logs and tests; no GPU work).
  * out[0]=variant chosen, out[1]=split_k (0 for STREAMK), out[2]=num_stages, out[3]=grid CTAs,
  * out[4]=dynamic shared memory bytes, out[5]=padded token count (MMA N), out[6]=K blocks of 128,
- * out[7]=tiles of 128 rows. Returns a status code. */
+ * out[7]=tiles along N (of out[3]/out[1] CTAs; a tile is at most 128 rows). Returns a status code. */
 int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8);
 
 /* ---- the element-wise kernels either side of the GEMM in a decoder layer -------------------
@@ -264,6 +264,10 @@ int hfrk_skinny_gemm_fp8_swiglu(const void* A, const void* W_gate_up, void* act_
  * writes (hf_rocm_kernels/benchmarks/skinny_gemm/grid_search.py); stands where the reference has
  * its hard-coded per-shape table (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:42-102). */
 int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages);
+/* The same with the tile height: tile_rows = W rows per CTA, 8..128 (0 = the built-in rule, which
+ * picks the smallest height that keeps the number of waves of the 128-row grid, so that the last
+ * wave loads every SM alike). All three 0 = drop the entry. */
+int hfrk_tuning_set_ex(int m, int n, int k, int split_k, int num_stages, int tile_rows);
 int hfrk_tuning_clear(void);
 
 /* How many clusters of `split` CTAs of the GEMM kernel with `smem_bytes` of dynamic shared memory

@@ -55,6 +55,18 @@ def test_plan_covers_the_sms(capi):
     for (m, n, k) in [(16, 28672, 4096), (4, 57344, 8192)]:
         p = capi.plan(m, n, k)
         assert p["split_k"] == 1 and p["num_stages"] == 6
+    # between one and two CTAs per SM without a split: shorter tiles even out the load
+    assert capi.plan(16, 28672, 4096)["tiles"] == 279 and capi.plan(4, 57344, 8192)["tiles"] == 448
+    assert capi.plan(17, 28672, 4096)["tiles"] == 224           # more than 16 tokens: 128-row tiles
+    try:
+        assert capi.lib.hfrk_tuning_set_ex(16, 4096, 4096, 0, 0, 64) == 0
+        assert capi.plan(16, 4096, 4096)["tiles"] == 64
+        assert capi.lib.hfrk_tuning_set_ex(16, 4096, 4096, 0, 0, 129) == 6
+        assert capi.lib.hfrk_tuning_set_ex(16, 4096, 4096, 0, 0, 4) == 6
+        assert capi.lib.hfrk_tuning_set_ex(16, 4096, 4096, 0, 0, 0) == 0     # drops the entry
+        assert capi.plan(16, 4096, 4096)["tiles"] == 32
+    finally:
+        capi.lib.hfrk_tuning_clear()
     # K tails and odd N round up; token padding is a multiple of 16
     p = capi.plan(5, 1000, 1040)
     assert p["tiles"] == 8 and p["k_blocks"] == 9 and p["m_pad"] == 16

@@ -221,6 +221,28 @@ def test_tuning_entry_changes_the_launch_not_the_result(capi, dev, checker):
     checker(tuned, a, w, scale, d_in, "tuned")
 
 
+@pytest.mark.parametrize("m,n,k,tile_rows", [(16, 1000, 1040, 97), (5, 4096, 4096, 118), (16, 28672, 4096, 0),
+                                              (3, 777, 512, 50), (16, 6144, 4096, 110), (16, 4096, 4096, 8),
+                                              (1, 20000, 1024, 0), (40, 2048, 1024, 72)])
+def test_tiles_of_fewer_than_128_rows(capi, dev, checker, m, n, k, tile_rows):
+    """Any tile height gives the same result: the lanes past the tile's rows are never stored.
+    tile_rows = 0 is the library's own choice, which is below 128 for the two shapes given."""
+    from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
+
+    case = wl.Case(8, 200 + tile_rows, "tile_rows", m, n, k, bias=(tile_rows % 2 == 0))
+    a, w, s, d_in, scale = _case_on_device(case, dev)
+    try:
+        if tile_rows:
+            assert capi.lib.hfrk_tuning_set_ex(m, n, k, 0, 0, tile_rows) == 0
+        plan = capi.plan(min(m, 64), n, k)
+        expect_rows = tile_rows if tile_rows else -(-n // 280)
+        assert plan["tiles"] == -(-n // expect_rows) and plan["ctas"] == plan["tiles"] * plan["split_k"]
+        out = _run_c(capi, a, w, s, d_in, case.m, case.n)
+    finally:
+        capi.lib.hfrk_tuning_clear()
+    checker(out, a, w, scale, d_in, f"tile_rows_{tile_rows}")
+
+
 @pytest.mark.parametrize("m", [64, 65, 70, 130])
 def test_token_counts_above_one_launch(capi, dev, checker, m):
     from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
