@@ -67,6 +67,7 @@ constexpr unsigned long long kTwoShotFromBytes = 1ull << 20;
 struct RowparDev {
     int rank, world;
     int two_shot;               // set per launch: 0 = every rank sends its partials to every peer
+    long long wait_cycles;      // how long a thread polls for a peer's cells before it gives up
     unsigned int elems_per_src;
     uint2* cells[kMaxWorld];
     unsigned int* call_index;   // local: number of completed calls on this communicator
@@ -181,7 +182,7 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
                     }
                 }
                 if (ready) break;
-                if (*abort_flag || clock64() - start > kWaitLimitCycles) {
+                if (*abort_flag || clock64() - start > rp.wait_cycles) {
                     *abort_flag = 1u;
                     record_timeout(kRolePeer);
                     ok = false;
@@ -226,7 +227,7 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
                     }
                 }
                 if (ready) break;
-                if (*abort_flag || clock64() - start > kWaitLimitCycles) {
+                if (*abort_flag || clock64() - start > rp.wait_cycles) {
                     *abort_flag = 1u;
                     record_timeout(kRolePeer);
                     ok = false;
@@ -260,7 +261,7 @@ __device__ __forceinline__ float round_trip_16(float x, int dtype) {
 }
 
 template <int kMode>
-__global__ void __launch_bounds__(kThreads, kMode == kModeRowPar ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, 2)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -810,8 +811,9 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan, in
     const int fixed_bytes = 1024 + kCtrlBytes + recv_bytes;
     const int max_stages_fit = (kSmemLimit - fixed_bytes) / stage_bytes;
     int stages = stages_req != 0 ? stages_req : (split > 1 ? 4 : 6);
-    if (stages_req == 0 && split > 1) {
-        // keep two CTAs on an SM when the receive buffer of a larger token count grows
+    if (stages_req == 0) {
+        // keep two CTAs on an SM when the activation tile or the receive buffer of a larger token
+        // count grows: with one CTA per SM a grid of 150-296 CTAs needs a second wave
         while (stages > 2 && 2 * (fixed_bytes + stages * stage_bytes + 1024) > 228 * 1024) --stages;
     }
     if (stages > max_stages_fit) stages = max_stages_fit;
@@ -1382,6 +1384,7 @@ extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfr
     hfrk_rowpar* g = new hfrk_rowpar();
     g->dev.rank = rank;
     g->dev.world = world;
+    g->dev.wait_cycles = hfrk::kWaitLimitCycles;
     g->dev.elems_per_src = static_cast<unsigned>(tiles) * m_cap * hfrk::kTileN;
     const size_t cells =
         (static_cast<size_t>(2) * (world + 1) * g->dev.elems_per_src * sizeof(uint2) + 255) / 256 * 256;
@@ -1457,6 +1460,13 @@ extern "C" int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* g, const void* A, const 
     return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k_shard, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
                              HFRK_VARIANT_CLUSTER, 0, 0, 0, hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream),
                              nullptr, &g->dev, g->mode);
+}
+
+extern "C" int hfrk_rowpar_set_wait_ms(hfrk_rowpar* g, int milliseconds) {
+    if (g == nullptr) return HFRK_BAD_WORLD;
+    if (milliseconds < 1 || milliseconds > 60000) return HFRK_INVALID_CONFIG;
+    g->dev.wait_cycles = static_cast<long long>(milliseconds) * 2000000ll;   // SM clock ticks at ~2 GHz
+    return HFRK_SUCCESS;
 }
 
 extern "C" int hfrk_rowpar_set_mode(hfrk_rowpar* g, int mode) {

@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
     "hfrk_swiglu_fp8", "hfrk_residual_rms", "hfrk_rowpar_set_mode",
     "hfrk_skinny_gemm_fp8_swiglu", "hfrk_skinny_gemm_fp8_host_async",
-    "hfrk_tuning_set_ex",
+    "hfrk_tuning_set_ex", "hfrk_rowpar_set_wait_ms",
 )
 
 
@@ -68,6 +68,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_rowpar_local_block.restype = vp
     lib.hfrk_rowpar_destroy.argtypes = [vp]
     lib.hfrk_rowpar_set_mode.argtypes = [vp, i32]
+    lib.hfrk_rowpar_set_wait_ms.argtypes = [vp, i32]
+    lib.hfrk_rowpar_set_wait_ms.restype = i32
     lib.hfrk_rowpar_set_mode.restype = i32
     lib.hfrk_skinny_gemm_fp8_rowpar.argtypes = [vp] + common + [vp]
     for name in ("hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect",

@@ -154,6 +154,12 @@ int hfrk_rowpar_destroy(hfrk_rowpar* group);
  * 1 MiB. Every rank of the group must use the same mode for the same call. */
 enum hfrk_rowpar_mode { HFRK_ROWPAR_AUTO = 0, HFRK_ROWPAR_ONE_SHOT = 1, HFRK_ROWPAR_TWO_SHOT = 2 };
 int hfrk_rowpar_set_mode(hfrk_rowpar* group, int mode);
+/* How long the kernel waits for a peer's partial sums before it gives up, in milliseconds of SM
+ * clock at ~2 GHz (1..60000; the default is about two seconds). A call whose peer does not
+ * deliver in time leaves D untouched for the elements concerned, sets the device status word
+ * (HFRK_DEVICE_TIMEOUT, role 4) and returns normally: the context stays usable, the group does
+ * not (its ranks no longer agree on the call number) and should be destroyed. */
+int hfrk_rowpar_set_wait_ms(hfrk_rowpar* group, int milliseconds);
 int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* group, const void* A_shard, const void* W_shard, void* D,
                                 const float* scale_dev, int m, int n, int k_shard, int64_t w_row_stride,
                                 int a_kind, int w_kind, int d_dtype, int accumulate, void* stream);
