@@ -105,6 +105,26 @@ def test_tuning_table_overrides_the_rule_per_shape(capi, tmp_path):
         tuning.clear_tuning()
 
 
+def test_plan_invariants_over_many_shapes(capi):
+    """Whatever the shape, a plan is launchable: the grid covers N, every CTA has K blocks to do,
+    the ring fits in shared memory, and the token padding matches the MMA."""
+    import random
+
+    rng = random.Random(11)
+    shapes = [(rng.randint(1, 64), rng.randint(1, 70000), 16 * rng.randint(1, 2048)) for _ in range(400)]
+    shapes += [(m, n, k) for m in (1, 16, 17, 64) for n in (1, 127, 128, 129, 18944, 19072, 37888) for k in (16, 128, 4096)]
+    for m, n, k in shapes:
+        p = capi.plan(m, n, k)
+        rows = -(-n // p["tiles"])                       # tile height the grid implies
+        assert 1 <= rows <= 128 and p["tiles"] * rows >= n and (p["tiles"] - 1) * rows < n, (m, n, k, p)
+        assert p["ctas"] == p["tiles"] * p["split_k"] and 1 <= p["split_k"] <= 16
+        assert p["split_k"] <= p["k_blocks"] == -(-k // 128)
+        assert 2 <= p["num_stages"] <= 12 and p["smem_bytes"] <= 227 * 1024
+        assert p["m_pad"] == 16 * (-(-m // 16))
+        if p["split_k"] > 1:
+            assert p["ctas"] <= 296, (m, n, k, p)        # a split grid must be resident at once
+
+
 def test_plan_rejects_bad_arguments(capi):
     out = (ctypes.c_int * 8)()
     assert capi.lib.hfrk_skinny_gemm_plan(0, 128, 128, 0, 0, 0, out) == 6
