@@ -209,10 +209,11 @@ def swiglu(gate_up: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, next_b
     rows, two_hidden = gate_up.shape
     assert gate_up.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (rows, two_hidden // 2)
     buffer_cols = 0 if next_buffer is None or rows == 0 else next_buffer.numel() // rows
-    return lib.hfrk_swiglu_fp8(gate_up.data_ptr(), scale.data_ptr(), out.data_ptr(),
-                               0 if next_buffer is None else next_buffer.data_ptr(), rows, two_hidden // 2,
-                               buffer_cols, out_kind(gate_up.dtype), fp8_kind(out.dtype), int(force_scalar),
-                               _stream_ptr(stream, gate_up.device))
+    with torch.cuda.device(gate_up.device):
+        return lib.hfrk_swiglu_fp8(gate_up.data_ptr(), scale.data_ptr(), out.data_ptr(),
+                                   0 if next_buffer is None else next_buffer.data_ptr(), rows, two_hidden // 2,
+                                   buffer_cols, out_kind(gate_up.dtype), fp8_kind(out.dtype), int(force_scalar),
+                                   _stream_ptr(stream, gate_up.device))
 
 
 def skinny_gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, act_out: torch.Tensor, scale: torch.Tensor,
@@ -225,11 +226,12 @@ def skinny_gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, act_out: torch.
     assert w_gate_up.shape[1] == k and w_gate_up.stride(1) == 1 and a.is_contiguous() and act_out.is_contiguous()
     assert tuple(act_out.shape) == (m, inter) and w_gate_up.shape[0] == 2 * inter
     buffer_cols = 0 if next_buffer is None else next_buffer.numel() // m
-    return lib.hfrk_skinny_gemm_fp8_swiglu(
-        a.data_ptr(), w_gate_up.data_ptr(), act_out.data_ptr(), scale.data_ptr(), act_scale.data_ptr(),
-        0 if next_buffer is None else next_buffer.data_ptr(), m, inter, k, w_gate_up.stride(0), fp8_kind(a.dtype),
-        fp8_kind(w_gate_up.dtype), out_kind(mid_dtype), fp8_kind(act_out.dtype), buffer_cols,
-        _stream_ptr(stream, a.device))
+    with torch.cuda.device(a.device):
+        return lib.hfrk_skinny_gemm_fp8_swiglu(
+            a.data_ptr(), w_gate_up.data_ptr(), act_out.data_ptr(), scale.data_ptr(), act_scale.data_ptr(),
+            0 if next_buffer is None else next_buffer.data_ptr(), m, inter, k, w_gate_up.stride(0),
+            fp8_kind(a.dtype), fp8_kind(w_gate_up.dtype), out_kind(mid_dtype), fp8_kind(act_out.dtype), buffer_cols,
+            _stream_ptr(stream, a.device))
 
 
 def residual_rms(input: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor],
@@ -241,11 +243,12 @@ def residual_rms(input: torch.Tensor, residual: torch.Tensor, weight: torch.Tens
     kind = OUT_SAME if output.dtype == input.dtype else (OUT_E4M3FNUZ if fp8_kind(output.dtype) == E4M3FNUZ
                                                          else OUT_E4M3FN)
     buffer_cols = 0 if next_buffer is None or rows == 0 else next_buffer.numel() // rows
-    return lib.hfrk_residual_rms(input.data_ptr(), residual.data_ptr(), weight.data_ptr(),
-                                 0 if scale is None else scale.data_ptr(), epsilon, output.data_ptr(),
-                                 0 if next_buffer is None else next_buffer.data_ptr(), rows, cols, buffer_cols,
-                                 out_kind(input.dtype), kind, num_threads, int(force_scalar),
-                                 _stream_ptr(stream, input.device))
+    with torch.cuda.device(input.device):
+        return lib.hfrk_residual_rms(input.data_ptr(), residual.data_ptr(), weight.data_ptr(),
+                                     0 if scale is None else scale.data_ptr(), epsilon, output.data_ptr(),
+                                     0 if next_buffer is None else next_buffer.data_ptr(), rows, cols, buffer_cols,
+                                     out_kind(input.dtype), kind, num_threads, int(force_scalar),
+                                     _stream_ptr(stream, input.device))
 
 
 def plan(m: int, n: int, k: int, variant: int = VARIANT_AUTO, split_k: int = 0, ctas_per_sm: int = 0) -> dict:
