@@ -1,5 +1,5 @@
-// Registers torch.ops._HFRK_C.skinny_gemm_tb, .swiglu and .residual_rms with the schemas of the
-// reference (csrc/torch_bindings.cpp:24-41 of huggingface/hf-rocm-kernels) and forwards to the C ABI
+// Registers torch.ops._HFRK_C.skinny_gemm_tb, .swiglu, .residual_rms and .increment with the schemas of
+// the reference (csrc/torch_bindings.cpp:20-41 of huggingface/hf-rocm-kernels) and forwards to the C ABI
 // of libhfrk_b200.so. This file is the only place where torch types meet the kernel library; it
 // does what csrc/op_src/skinny_gemm/skinny_gemm_binding.cu:16-42 does in the reference: pull
 // pointers, shapes and the W pitch out of the tensors, pick the current stream of A's device and
@@ -131,7 +131,12 @@ void residual_rms(torch::Tensor& input, torch::Tensor& residual, torch::Tensor& 
     TORCH_CHECK(status == HFRK_SUCCESS, "residual_rms: status ", status, " (", hfrk_last_error(), ")");
 }
 
+// The reference's registration smoke test (csrc/op_src/increment/increment_op.cu:3): x += 1 through ATen.
+void increment(torch::Tensor& x) { x.add_(1); }
+
 TORCH_LIBRARY(_HFRK_C, ops) {
+    ops.def("increment(Tensor! x) -> ()");
+    ops.impl("increment", torch::kCUDA, &increment);
     ops.def(
         "residual_rms(Tensor input, Tensor! residual, Tensor weight, Tensor scale_tensor, float epsilon, Tensor! "
         "output, Tensor! next_buffer, int num_threads, bool force_scalar) -> ()");

@@ -303,6 +303,18 @@ def test_residual_rms_empty_and_invalid_inputs(capi, dev):
                                        torch.empty((2, 0), dtype=torch.float16, device=dev), 0, False)
 
 
+def test_increment_adds_one_in_place(native_build, dev):
+    """The reference's tests/test_increment.py:8-12."""
+    from hf_rocm_kernels import increment
+
+    x = torch.rand(size=(128,), device=dev)
+    y = x.clone()
+    increment(x)
+    assert x.eq(y + 1).all()
+    with pytest.raises(AssertionError):
+        increment(torch.zeros(4))
+
+
 # ------------------------------------------------------- gate/up GEMM with swiglu in its epilogue
 @pytest.mark.parametrize("act_dtype,fp8_dtype", [(torch.float16, torch.float8_e4m3fnuz),
                                                  (torch.bfloat16, torch.float8_e4m3fn)])

@@ -52,7 +52,9 @@ def test_elementwise_operators_keep_the_reference_surface(pkg):
     from hf_rocm_kernels.operators.swiglu.binding import _swiglu
 
     assert pkg.swiglu is swiglu and pkg.residual_rms is residual_rms
-    assert set(pkg.__all__) == {"residual_rms", "swiglu", "skinny_gemm"}
+    assert pkg.__all__ == ["increment", "residual_rms", "swiglu", "skinny_gemm"]      # the reference's list
+    assert str(torch.ops._HFRK_C.increment.default._schema) == str(
+        torch._C.parse_schema("_HFRK_C::increment(Tensor! x) -> ()"))
     assert list(inspect.signature(swiglu).parameters)[:5] == [
         "gate_up_proj", "scale_tensor", "next_buffer", "force_scalar", "num_threads"]
     assert list(inspect.signature(_swiglu).parameters) == [
