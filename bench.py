@@ -285,6 +285,20 @@ def run_ours(args):
                            "hbm_tbps": round(c.algorithmic_bytes() / us / 1e6, 3),
                            "weight_tbps": round(c.weight_bytes / us / 1e6, 3)})
 
+    # ---- configuration 2 with all of N on this GPU (its g = 1 column): the Llama-3-70B projections
+    detail_70b = None
+    if world == 1 and not args.no_detail:
+        detail_70b = []
+        for c in wl.cases(2):
+            inp = wl.make_inputs(c, device=str(dev))
+            it = {"case": c, "a": inp["a"], "w": inp["w"], "scale": inp["scale"],
+                  "d0": torch.zeros((c.m, c.n), dtype=torch.bfloat16, device=dev)}
+            us = time_case_rotating(it, hf_rocm_kernels.skinny_gemm, torch, warmups=4, iters=12)
+            detail_70b.append({"case": c.name, "us_per_call": round(us, 2),
+                               "weight_tbps": round(c.weight_bytes / us / 1e6, 3)})
+            del it, inp
+            torch.cuda.empty_cache()
+
     layer_block = mlp_block_detail(torch, dev) if world == 1 and not args.no_detail else None
 
     status_code, status_word = capi.device_status(clear=True)
@@ -329,6 +343,8 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_baseline(torch, wl)
         if detail is not None:
             line["detail"] = detail
+        if detail_70b is not None:
+            line["detail_llama3_70b"] = detail_70b
         if layer_block is not None:
             line["layer_block"] = layer_block
         if multi is not None:

@@ -282,7 +282,11 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // Split-K reduction geometry: the m x 128 tile is cut into `split` element ranges of `chunk`
     // floats (a multiple of 4, so that every range is a 16-byte-aligned bulk copy).
     const int total = p.m * kTileN;
-    const uint32_t chunk = ((static_cast<uint32_t>(total) + p.split - 1) / p.split + 3u) & ~3u;
+    // SwiGLU: a range is whole token rows of the tile (ceil(m / split) of them), so that the gate
+    // half and the up half of a column always meet in the same CTA.
+    const uint32_t chunk = kMode == kModeSwiglu
+                               ? static_cast<uint32_t>(kTileN) * ((static_cast<uint32_t>(p.m) + p.split - 1) / p.split)
+                               : ((static_cast<uint32_t>(total) + p.split - 1) / p.split + 3u) & ~3u;
 
     constexpr bool kRowPar = kMode == kModeRowPar;
     const int warp = threadIdx.x >> 5;
@@ -464,7 +468,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (threadIdx.x == 0) stamp(p, 5);
         tcgen05_fence_after_sync();
         float* const partial = reinterpret_cast<float*>(ring_ptr);  // the ring is idle by now
-        if (kMode == kModeSwiglu) {
+        if (kMode == kModeSwiglu && direct) {
             // Lanes 0..63 hold gate columns, lanes 64..127 the matching up columns. The projection is
             // rounded to the 16-bit type first, as the unfused chain stores it, so both give the same
             // bytes. The activation is shared out by tokens: the gate thread of a column takes tokens
@@ -517,12 +521,6 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                         *reinterpret_cast<const uint4*>(out_tile + token * kHalfTile + piece * 16);
                 }
             }
-            // the next GEMM adds into this buffer
-            const size_t vecs = static_cast<size_t>(p.zero_bytes / 16);
-            for (size_t i = static_cast<size_t>(blockIdx.x) * kEpilogueThreads + threadIdx.x; i < vecs;
-                 i += static_cast<size_t>(gridDim.x) * kEpilogueThreads) {
-                reinterpret_cast<uint4*>(p.zero_ptr)[i] = make_uint4(0, 0, 0, 0);
-            }
         } else if (ok) {
             for (int c = 0; c < p.m_pad / 16; ++c) {
                 uint32_t v[16];
@@ -574,7 +572,64 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
             bool landed = ok && mbar_wait_bounded(recv_bar, 0u, &ctrl->abort, kRoleEpilogue);
             landed = __all_sync(0xffffffffu, landed);
-            if (landed) {
+            if (kMode == kModeSwiglu) {
+                // This CTA owns `rows` whole token rows of the tile, starting at token t0; thread
+                // tid holds lane tid of each. Same activation as in the unsplit case: the gate lane
+                // of a column takes the first half of the tokens, the up lane the second half.
+                const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
+                const int per_owner = static_cast<int>(chunk) / kTileN;          // <= 8 for m <= 16, split >= 2
+                const int t0 = rank * per_owner;
+                const int rows = landed ? (p.m - t0 < per_owner ? p.m - t0 : per_owner) : 0;   // may be <= 0
+                const int first_half = (per_owner + 1) / 2;
+                constexpr int kPitch = 5;                                        // floats per column and half
+                float* const handed = partial + static_cast<size_t>(p.split) * chunk;   // past the staged tile
+                uint8_t* const out_tile = reinterpret_cast<uint8_t*>(handed + 2 * kHalfTile * kPitch);  // [8][64]
+                const int col_in_tile = nl & (kHalfTile - 1);
+                const int half = nl >> 6;
+                float y[kOwned];
+#pragma unroll
+                for (int it = 0; it < kOwned; ++it) {
+                    float sum = 0.0f;
+                    if (it < rows) {
+                        for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + it * kTileN + nl];
+                    }
+                    y[it] = round_trip_16(sum * scale, p.d_dtype);
+                }
+#pragma unroll
+                for (int it = 0; it < kOwned; ++it) {
+                    const bool give = half == 0 ? it >= first_half : it < first_half;
+                    if (give && it < per_owner) {
+                        const int slot_in_half = half == 0 ? it - first_half : it;
+                        handed[((1 - half) * kHalfTile + col_in_tile) * kPitch + slot_in_half] = y[it];
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+                const float inv_act = 1.0f / __ldg(p.act_scale);
+#pragma unroll
+                for (int it = 0; it < kOwned; ++it) {
+                    const bool mine = half == 0 ? it < first_half : it >= first_half;
+                    if (mine && it < rows) {
+                        const int slot_in_half = half == 0 ? it : it - first_half;
+                        const float other = handed[(half * kHalfTile + col_in_tile) * kPitch + slot_in_half];
+                        const float gate = half == 0 ? y[it] : other;
+                        const float up = half == 0 ? other : y[it];
+                        float t = (gate / (1.0f + expf(-gate))) * up * inv_act;
+                        if (p.act_fnuz) t *= 2.0f;
+                        uint8_t byte = static_cast<uint8_t>(pack_e4m3x2(t, 0.0f) & 0xffu);
+                        if (p.act_fnuz && byte == 0x80u) byte = 0;
+                        out_tile[it * kHalfTile + col_in_tile] = byte;
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+                if (nl < 4 * rows) {
+                    const int row = nl >> 2, piece = nl & 3;
+                    const int col = static_cast<int>(blockIdx.x) * kHalfTile + piece * 16;
+                    if (col < p.act_cols) {
+                        *reinterpret_cast<uint4*>(p.act_out + static_cast<size_t>(t0 + row) * p.act_cols + col) =
+                            *reinterpret_cast<const uint4*>(out_tile + row * kHalfTile + piece * 16);
+                    }
+                }
+            } else if (landed) {
                 const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
                 float own[kOwned];
                 uint32_t slot[kOwned];
@@ -620,6 +675,15 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
             // the staged partial tile must outlive the copies that read it
             if (threadIdx.x == 0) bulk_copies_source_done();
+        }
+        if (kMode == kModeSwiglu) {
+            // the next GEMM adds into this buffer: the whole grid clears it
+            const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+            const size_t ctas = static_cast<size_t>(gridDim.x) * gridDim.y;
+            const size_t vecs = static_cast<size_t>(p.zero_bytes / 16);
+            for (size_t i = cta * kEpilogueThreads + threadIdx.x; i < vecs; i += ctas * kEpilogueThreads) {
+                reinterpret_cast<uint4*>(p.zero_ptr)[i] = make_uint4(0, 0, 0, 0);
+            }
         }
     }
 
@@ -860,6 +924,8 @@ int prepare_device_once() {
                                        cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeSwiglu>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeSwiglu>,
+                                       cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<1>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_streamk_kernel<2>,
@@ -1147,11 +1213,12 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
 // zeroing of the down projection's accumulate buffer in the epilogue: one launch where the chain
 // has GEMM + swiglu. W is [2 * inter, k]: `inter` gate rows, then `inter` up rows. Tile t of the
 // grid takes gate rows [64t, 64t + 64) and up rows [inter + 64t, inter + 64t + 64), so that both
-// halves of every output column meet in one CTA. No K split: the epilogue needs whole sums.
+// halves of every output column meet in one CTA. With a K split the cluster's reduction hands every
+// CTA whole token rows of the tile (not arbitrary element ranges), so the halves still meet.
 int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float* scale_dev,
                        const float* act_scale_dev, void* next_buffer, int m, int inter, int k, int64_t w_row_stride,
-                       int a_kind, int w_kind, int mid_dtype, int out_kind, int64_t buffer_cols, int use_pdl,
-                       cudaStream_t stream) {
+                       int a_kind, int w_kind, int mid_dtype, int out_kind, int64_t buffer_cols, int split_req,
+                       int use_pdl, cudaStream_t stream) {
     if (A == nullptr || W == nullptr || act_out == nullptr || scale_dev == nullptr || act_scale_dev == nullptr)
         return HFRK_INVALID_CONFIG;
     if (m <= 0 || inter <= 0 || k <= 0 || buffer_cols < 0) return HFRK_INVALID_CONFIG;
@@ -1175,8 +1242,20 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
                         static_cast<uint64_t>(w_row_stride), kHalfTile, &tmap_w);
     if (rc != HFRK_SUCCESS) return rc;
     Plan plan;
-    rc = make_plan(m, 2 * inter, k, /*split_req=*/1, /*stages_req=*/0, &plan, kAutoTileRowsOff);
+    rc = make_plan(m, 2 * inter, k, split_req, /*stages_req=*/0, &plan, kAutoTileRowsOff);
     if (rc != HFRK_SUCCESS) return rc;
+    if (plan.split > 1) {
+        // the receive buffer holds whole token rows per owner: ceil(m / split) rows of 128 floats
+        const int plain_chunk = (((m * kTileN + plan.split - 1) / plan.split) + 3) & ~3;
+        const int row_chunk = kTileN * ((m + plan.split - 1) / plan.split);
+        plan.smem_bytes += plan.split * (row_chunk - plain_chunk) * 4;
+        const int stage_bytes = kWStageBytes + plan.m_pad * kBlockK;
+        while (plan.stages > 2 && 2 * (plan.smem_bytes + 1024) > 228 * 1024) {
+            --plan.stages;
+            plan.smem_bytes -= stage_bytes;
+        }
+        if (plan.smem_bytes > kSmemLimit) return HFRK_INVALID_CONFIG;
+    }
     rc = get_tensor_map(A, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                         static_cast<uint32_t>(plan.m_pad), &tmap_a);
     if (rc != HFRK_SUCCESS) return rc;
@@ -1191,7 +1270,7 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
     p.m_pad = plan.m_pad;
     p.tile_rows = kTileN;
     p.num_kblocks = plan.num_kblocks;
-    p.split = 1;
+    p.split = plan.split;
     p.stages = plan.stages;
     p.d_dtype = mid_dtype;
     p.accumulate = 0;
@@ -1204,12 +1283,19 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
 
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(static_cast<unsigned>((inter + kHalfTile - 1) / kHalfTile), 1, 1);
+    cfg.gridDim = dim3(static_cast<unsigned>((inter + kHalfTile - 1) / kHalfTile), static_cast<unsigned>(plan.split), 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     unsigned num_attrs = 0;
+    if (plan.split > 1) {
+        attrs[num_attrs].id = cudaLaunchAttributeClusterDimension;
+        attrs[num_attrs].val.clusterDim.x = 1;
+        attrs[num_attrs].val.clusterDim.y = static_cast<unsigned>(plan.split);
+        attrs[num_attrs].val.clusterDim.z = 1;
+        ++num_attrs;
+    }
     if (use_pdl) {
         attrs[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[num_attrs].val.programmaticStreamSerializationAllowed = 1;
@@ -1494,7 +1580,7 @@ extern "C" int hfrk_skinny_gemm_fp8_swiglu(const void* A, const void* W_gate_up,
                                            int m, int inter, int k, int64_t w_row_stride, int a_kind, int w_kind,
                                            int mid_dtype, int out_kind, int64_t buffer_cols, void* stream) {
     return hfrk::launch_gemm_swiglu(A, W_gate_up, act_out, scale_dev, act_scale_dev, next_buffer, m, inter, k,
-                                    w_row_stride, a_kind, w_kind, mid_dtype, out_kind, buffer_cols,
+                                    w_row_stride, a_kind, w_kind, mid_dtype, out_kind, buffer_cols, /*split_req=*/0,
                                     hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream));
 }
 

@@ -255,8 +255,9 @@ int hfrk_residual_rms(const void* input, void* residual, const void* weight, con
  * chain uses); a CTA's tile is 64 gate rows plus the matching 64 up rows. mid_dtype (HFRK_F16 or
  * HFRK_BF16) is the type the unfused chain would have stored the projection in: the epilogue
  * rounds to it before the activation so that fused and unfused results are identical bytes.
- * Limits: m <= 16 (HFRK_TOO_LARGE), inter % 16 == 0, no bias, no K split (meant for gate/up
- * matrices of at least ~148 tiles of 64 columns; narrower shards are faster unfused).
+ * Limits: m <= 16 (HFRK_TOO_LARGE), inter % 16 == 0, no bias. K is split over a cluster as in the
+ * plain GEMM when the matrix has too few tiles for the SMs; the reduction then hands every CTA
+ * whole token rows, so the result does not depend on the split.
  * act_out and next_buffer 16-byte aligned. No counterpart in the reference, whose
  * combined_ops/llama_mlp.py:29-47 runs the two kernels one after the other. */
 int hfrk_skinny_gemm_fp8_swiglu(const void* A, const void* W_gate_up, void* act_out,

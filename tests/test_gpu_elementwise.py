@@ -319,7 +319,10 @@ def test_increment_adds_one_in_place(native_build, dev):
 @pytest.mark.parametrize("act_dtype,fp8_dtype", [(torch.float16, torch.float8_e4m3fnuz),
                                                  (torch.bfloat16, torch.float8_e4m3fn)])
 @pytest.mark.parametrize("m,inter,k", [(16, 14336, 4096), (1, 14336, 4096), (5, 1040, 256), (16, 64, 128),
-                                       (3, 4144, 512), (9, 28672, 8192), (16, 16, 2048)])
+                                       (3, 4144, 512), (9, 28672, 8192), (16, 16, 2048),
+                                       # K split over a cluster: 5, 5, 8 and 12 CTAs per tile; owners with
+                                       # four, one, one-or-none and two-one-or-none token rows
+                                       (16, 3584, 8192), (1, 3584, 8192), (7, 2048, 4096), (13, 1024, 8192)])
 def test_fused_gemm_swiglu_writes_the_bytes_of_the_two_launches(capi, dev, m, inter, k, act_dtype, fp8_dtype):
     """One launch (GEMM with the activation in its epilogue) against GEMM into a 16-bit buffer
     followed by the swiglu kernel: identical bytes, zeroed buffer, nothing written out of bounds."""
@@ -417,6 +420,7 @@ def test_llama_mlp_chain_equals_its_parts_and_tracks_the_unquantised_block(capi,
     from hf_rocm_kernels.combined_ops import can_fuse_swiglu
 
     assert can_fuse_swiglu(tokens, hidden, inter)          # so `chain` ran the three-launch form
+    assert not can_fuse_swiglu(17, hidden, inter) and not can_fuse_swiglu(4, hidden, 1000)
     for fuse in (False, True):
         out_f, res_f = llama_mlp_combined_ops(p["attn"], p["residual"].clone(), p["rms_w"], 1e-5, p["q_gu"].t(),
                                               p["in_scale_gu"], p["out_scale_gu"], p["q_dn"].t(), p["in_scale_dn"],
