@@ -69,8 +69,7 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
 // HFRK_PDL=0. The kernels launched this way call griddepcontrol.wait before their first load.
 template <typename Kernel, typename... Args>
 int launch_elementwise(Kernel kernel, unsigned grid, unsigned block, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(block, 1, 1);
     cfg.stream = stream;

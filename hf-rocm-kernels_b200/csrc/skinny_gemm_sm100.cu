@@ -1087,8 +1087,7 @@ int launch_streamk(const void* A, const void* W, void* D, const float* scale_dev
         p.counters = counters;
         p.stamps = stamps;
 
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(plan.grid), 1, 1);
         cfg.blockDim = dim3(kThreads, 1, 1);
         cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
@@ -1178,8 +1177,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
             if (static_cast<unsigned long long>(tiles) * mc * kTileN > p.rp.elems_per_src) return HFRK_TOO_LARGE;
         }
 
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(plan.tiles), static_cast<unsigned>(plan.split), 1);
         cfg.blockDim = dim3(kThreads, 1, 1);
         cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
@@ -1281,8 +1279,7 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
     p.zero_ptr = static_cast<uint8_t*>(next_buffer);
     p.zero_bytes = zero_bytes;
 
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>((inter + kHalfTile - 1) / kHalfTile), static_cast<unsigned>(plan.split), 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
@@ -1433,8 +1430,7 @@ extern "C" int hfrk_skinny_gemm_fp8_noalloc(const void* A, const void* W, void* 
     p.counters = counters;
     p.stamps = nullptr;
 
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(plan.grid), 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
@@ -1707,8 +1703,7 @@ extern "C" int hfrk_max_active_clusters(int split, int smem_bytes, int* clusters
         return HFRK_INVALID_CONFIG;
     int rc = hfrk::prepare_device_once();
     if (rc != HFRK_SUCCESS) return rc;
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, static_cast<unsigned>(split), 1);
     cfg.blockDim = dim3(hfrk::kThreads, 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
