@@ -154,6 +154,6 @@ TORCH_LIBRARY(_HFRK_C, ops) {
 // `import hf_rocm_kernels._HFRK_C` only has to load this shared object so that the static
 // registration above runs; the module itself is empty.
 PyMODINIT_FUNC PyInit__HFRK_C(void) {
-    static struct PyModuleDef module = {PyModuleDef_HEAD_INIT, "_HFRK_C", nullptr, 0, nullptr};
+    static struct PyModuleDef module = {PyModuleDef_HEAD_INIT, "_HFRK_C", nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr};
     return PyModule_Create(&module);
 }
