@@ -1,3 +1,6 @@
-from .wrapped import increment
+"""increment: the registration smoke test of the extension."""
+from . import wrapped as _wrapped
 
-__all__ = ["increment"]
+increment = _wrapped.increment
+
+__all__ = ("increment",)

@@ -1,9 +1,9 @@
-"""Bridge to the registered torch op, as in the reference's
-``hf_rocm_kernels/operators/increment/binding.py:6-7``."""
-import torch
+"""Hands the tensor to ``torch.ops._HFRK_C.increment`` (the reference does the same in
+``operators/increment/binding.py``); importing the extension module registers the op."""
+from torch import Tensor, ops
 
-import hf_rocm_kernels._HFRK_C  # noqa: F401  (loads the extension that registers torch.ops._HFRK_C)
+from hf_rocm_kernels import _HFRK_C as _extension  # noqa: F401
 
 
-def _increment(x: torch.Tensor) -> None:
-    torch.ops._HFRK_C.increment(x)
+def _increment(x: Tensor) -> None:
+    ops._HFRK_C.increment(x)

@@ -1,11 +1,12 @@
-"""``increment``: the reference's build smoke test (``operators/increment/wrapped.py:6-9``), a
-one-line ATen op behind the same registration path as the real operators."""
-import torch
+"""``increment``: one ATen ``add_`` behind the same registration path as the real operators. The
+reference ships it as its build smoke test (``operators/increment/wrapped.py``)."""
+from torch import Tensor
 
-from .binding import _increment
+from . import binding
 
 
-def increment(x: torch.Tensor) -> None:
-    """Adds 1 to the given GPU-resident tensor in place."""
-    assert x.device.type == "cuda", f"Expected x.device to be of type cuda but got {x.device.type = }"
-    _increment(x)
+def increment(x: Tensor) -> None:
+    """x <- x + 1, in place; ``x`` must live on a CUDA device."""
+    if x.device.type != "cuda":
+        raise AssertionError(f"increment works on CUDA tensors, got one on {x.device}")
+    binding._increment(x)

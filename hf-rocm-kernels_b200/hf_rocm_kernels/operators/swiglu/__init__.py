@@ -1,4 +1,9 @@
-from .wrapped import swiglu
-from .reference import reference_swiglu, generate_swiglu_data
+"""swiglu: the operator, its torch statement and its input generator."""
+from . import reference as _reference
+from . import wrapped as _wrapped
 
-__all__ = ["swiglu", "reference_swiglu", "generate_swiglu_data"]
+swiglu = _wrapped.swiglu
+reference_swiglu = _reference.reference_swiglu
+generate_swiglu_data = _reference.generate_swiglu_data
+
+__all__ = ("swiglu", "reference_swiglu", "generate_swiglu_data")
