@@ -91,3 +91,38 @@ def test_16_bit_helpers_round_like_the_hardware():
     assert np.array_equal(ew.add16(a, b, F16), a + b)
     assert np.array_equal(ew.mul16(a, b, F16), a * b)
     assert ew.fp8_step_distance(np.array([0x01, 0x81, 0x7E]), np.array([0x00, 0x01, 0x7D])).tolist() == [1, 2, 1]
+
+
+def test_quantiser_is_idempotent_on_its_own_grid():
+    """Every finite e4m3fn value encodes back to its own byte, for both output kinds (the fnuz
+    form drops the sign of zero and halves the value a byte is worth)."""
+    from oracle import fp8_table
+
+    codes = np.array([b for b in range(256) if b not in (0x7F, 0xFF)], dtype=np.uint8)
+    values = fp8_table(E4M3FN)[codes]
+    again = ew.fp8_bytes(values, 1.0, E4M3FN)
+    assert np.array_equal(again, codes)
+    as_fnuz = ew.fp8_bytes(values / 2, 1.0, E4M3FNUZ)          # a fnuz byte is worth half the fn byte
+    assert np.array_equal(as_fnuz, np.where(codes == 0x80, 0, codes))
+    # saturation: never the NaN pattern, in either kind
+    big = np.array([1e9, -1e9, 449.0, -449.0, 460.0], dtype=np.float32)
+    assert set(ew.fp8_bytes(big, 1.0, E4M3FN).tolist()) == {0x7E, 0xFE}
+    assert set(ew.fp8_bytes(big, 1.0, E4M3FNUZ).tolist()) == {0x7E, 0xFE}
+
+
+def test_residual_rms_forms_share_the_sum_and_scale_invariance():
+    """Both restatements update the residual identically; doubling the scale with the fnuz kind
+    gives the bytes of the e4m3fn kind (up to the sign of zero): the identity the drop-in relies on."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((6, 256)).astype(np.float16)
+    res = rng.standard_normal((6, 256)).astype(np.float16)
+    w = rng.standard_normal(256).astype(np.float16)
+    for form in ("kernel", "torch"):
+        out_fn, sum_fn = ew.reference_residual_rms(x, res, w, 1e-5, 0.02, F16, E4M3FN, form=form)
+        out_fnuz, sum_fnuz = ew.reference_residual_rms(x, res, w, 1e-5, 0.04, F16, E4M3FNUZ, form=form)
+        assert np.array_equal(sum_fn.view(np.uint16), (x + res).view(np.uint16))
+        assert np.array_equal(sum_fn.view(np.uint16), sum_fnuz.view(np.uint16))
+        assert np.array_equal(np.where(out_fn == 0x80, 0, out_fn), out_fnuz)
+    zero = np.zeros((2, 64), dtype=np.float16)
+    out, _ = ew.reference_residual_rms(zero, zero, np.ones(64, dtype=np.float16), 1e-5, None, F16)
+    assert np.array_equal(out.view(np.uint16), zero.view(np.uint16)), "epsilon keeps an all-zero row finite"
