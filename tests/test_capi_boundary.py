@@ -184,3 +184,34 @@ def test_status_names_cover_the_header(capi):
     codes = dict((int(v), k) for k, v in re.findall(r"HFRK_([A-Z_0-9]+) = (\d+)", text.split("enum hfrk_fp8_kind")[0]))
     for code, name in codes.items():
         assert capi.STATUS_NAMES[code] == name
+
+
+def test_a_plain_c_program_links_against_the_library(capi, tmp_path):
+    """The boundary is C: the header compiles as C99 and a C program with no C++ runtime of its own
+    links the shared library and calls it (the calls chosen need no GPU)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    source = tmp_path / "caller.c"
+    source.write_text(
+        '#include <stdio.h>\n#include "hfrk_b200.h"\n'
+        "int main(void) {\n"
+        "    int plan[8];\n"
+        "    int rc = hfrk_skinny_gemm_plan(16, 4096, 4096, HFRK_VARIANT_AUTO, 0, 0, plan);\n"
+        '    printf("%d %d %d %d %s\\n", hfrk_version(), rc, plan[1], plan[3], hfrk_last_error());\n'
+        "    return rc == HFRK_SUCCESS ? 0 : 1;\n"
+        "}\n")
+    lib_dir = os.path.dirname(capi.library_path())
+    exe = tmp_path / "caller"
+    build = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-I", os.path.dirname(HEADER), str(source),
+                            "-o", str(exe), "-L", lib_dir, "-l:libhfrk_b200.so", f"-Wl,-rpath,{lib_dir}"],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, run.stderr
+    version, rc, split, ctas = run.stdout.split()[:4]
+    assert int(version) == capi.lib.hfrk_version() and int(rc) == 0
+    assert int(split) == capi.plan(16, 4096, 4096)["split_k"] and int(ctas) == capi.plan(16, 4096, 4096)["ctas"]
