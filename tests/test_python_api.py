@@ -206,3 +206,34 @@ def test_workload_configurations():
     assert wl.n_split_rows(10240, 8, 3) == (3840, 5120) and wl.k_split_cols(28672, 8, 7) == (25088, 28672)
     with pytest.raises(ValueError):
         wl.n_split_rows(1000, 3, 0)
+
+
+def test_the_package_fails_loudly_without_its_native_library(native_build, tmp_path):
+    """No CPU or PyTorch fallback: with the shared library out of reach the import raises and names
+    the build command; with it in place but no GPU, the operators refuse CPU tensors."""
+    import os
+    import shutil
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "hf-rocm-kernels_b200", "hf_rocm_kernels")
+    copy = tmp_path / "hf_rocm_kernels"
+    shutil.copytree(src, copy, ignore=shutil.ignore_patterns("*.so", "__pycache__"))
+    probe = ("import sys; sys.path.insert(0, sys.argv[1])\n"
+             "try:\n    import hf_rocm_kernels\nexcept ImportError as e:\n    print('IMPORT_ERROR', e)\n"
+             "else:\n    print('IMPORTED')\n")
+    out = subprocess.run([sys.executable, "-c", probe, str(tmp_path)], capture_output=True, text=True, timeout=300)
+    assert "IMPORT_ERROR" in out.stdout, out.stdout + out.stderr
+
+    from hf_rocm_kernels import residual_rms, skinny_gemm, swiglu
+
+    a = torch.zeros((4, 256), dtype=torch.float8_e4m3fn)
+    w = torch.zeros((128, 256), dtype=torch.float8_e4m3fn)
+    with pytest.raises(AssertionError, match="cuda"):
+        skinny_gemm(a, w.t(), torch.ones(1), torch.zeros((4, 128), dtype=torch.bfloat16))
+    with pytest.raises(AssertionError, match="cuda"):
+        swiglu(torch.zeros((2, 64), dtype=torch.float16), torch.ones(1))
+    with pytest.raises(AssertionError, match="cuda"):
+        residual_rms(torch.zeros((2, 64), dtype=torch.float16), torch.zeros((2, 64), dtype=torch.float16),
+                     torch.ones(64, dtype=torch.float16), 1e-5)
