@@ -435,3 +435,59 @@ def test_full_size_properties(capi, dev):
     perm = torch.randperm(n, device=dev, generator=gen)
     assert torch.equal(_run_c(capi, a, w[perm].contiguous(), s1, None, m, n), out1[:, perm])
     assert capi.device_status(clear=True)[0] == 0
+
+
+def test_calls_from_several_threads_on_several_streams(capi, dev):
+    """Four host threads, each with its own stream and its own shapes, launch interleaved GEMMs,
+    fused gate/up launches and element-wise kernels; every result must equal the one computed
+    serially beforehand (the library's caches and tables are shared between the threads)."""
+    import threading
+
+    from hf_rocm_kernels import residual_rms, skinny_gemm, swiglu
+    from hf_rocm_kernels.combined_ops import skinny_gemm_swiglu
+
+    torch.manual_seed(77)
+    jobs = []
+    for t, (m, n, k) in enumerate([(16, 4096, 4096), (3, 1000, 1040), (8, 6144, 2048), (1, 2048, 8192)]):
+        a = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        w = torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        scale = torch.tensor([1e-4], device=dev)
+        x = torch.randn(m, 1024, device=dev).half()
+        r = torch.randn(m, 1024, device=dev).half()
+        g = torch.ones(1024, device=dev).half()
+        inter = (n // 2) // 16 * 16
+        jobs.append(dict(a=a, w=w, scale=scale, x=x, r=r, g=g, inter=inter, m=m, n=n))
+
+    def run(job, stream):
+        with torch.cuda.stream(stream):
+            out = torch.zeros((job["m"], job["n"]), dtype=torch.bfloat16, device=dev)
+            skinny_gemm(job["a"], job["w"].t(), job["scale"], out)
+            act = skinny_gemm_swiglu(job["a"], job["w"][:2 * job["inter"]].t(), job["scale"], job["scale"] * 100)
+            normed, res = residual_rms(job["x"].clone(), job["r"].clone(), job["g"], 1e-5, job["scale"] * 1e4)
+            sw = swiglu(out[:, :2 * (job["n"] // 2)].contiguous(), job["scale"] * 100)
+        stream.synchronize()
+        return [out, act.view(torch.uint8), normed.view(torch.uint8), res, sw.view(torch.uint8)]
+
+    expect = [run(job, torch.cuda.current_stream(dev)) for job in jobs]
+    results = [None] * len(jobs)
+    errors = []
+
+    def worker(i):
+        try:
+            torch.cuda.set_device(dev)
+            stream = torch.cuda.Stream(dev)
+            for _ in range(6):
+                results[i] = run(jobs[i], stream)
+        except Exception as exc:   # surfaced below: a thread must not die silently
+            errors.append((i, repr(exc)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(jobs))]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join(timeout=120)
+    assert not errors, errors
+    torch.cuda.synchronize()
+    assert capi.device_status(clear=True)[0] == 0
+    for i, (want, got) in enumerate(zip(expect, results)):
+        assert got is not None and all(torch.equal(a, b) for a, b in zip(want, got)), f"job {i} differs"
