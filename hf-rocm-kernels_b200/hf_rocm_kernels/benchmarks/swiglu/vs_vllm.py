@@ -13,12 +13,17 @@ from hf_rocm_kernels.utils.benchmarking import Bench
 
 
 def load_vllm_ops():
-    """vLLM's custom-op module, or None with the reason printed."""
+    """The three vLLM kernels the comparisons need (``silu_and_mul``, ``scaled_fp8_quant``,
+    ``fused_add_rms_norm``) as attributes of one object, or None with the reason printed. vLLM has
+    moved ``silu_and_mul`` between its Python wrapper module and ``torch.ops._C`` over time."""
     try:
+        import types
+
         import vllm._custom_ops as ops
 
-        _ = ops.silu_and_mul, ops.scaled_fp8_quant
-        return ops
+        silu = getattr(ops, "silu_and_mul", None) or torch.ops._C.silu_and_mul
+        return types.SimpleNamespace(silu_and_mul=silu, scaled_fp8_quant=ops.scaled_fp8_quant,
+                                     fused_add_rms_norm=ops.fused_add_rms_norm)
     except BaseException as error:   # vLLM raises more than ImportError when its extension is absent
         print(f"vLLM custom ops unavailable ({type(error).__name__}: {error}); only this library is timed.")
         return None

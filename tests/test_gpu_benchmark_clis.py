@@ -27,6 +27,8 @@ COMMANDS = [
     ("hf_rocm_kernels.benchmarks.residual_rms.vs_reference", ["-r", "1", "16", "-c", "1024", "-b", "256"], "Vectorized"),
     ("hf_rocm_kernels.benchmarks.residual_rms.vs_reference", ["-r", "4", "-c", "1024", "--fp16-output"], "Vectorized"),
     ("hf_rocm_kernels.benchmarks.residual_rms.nb_threads", ["-r", "4", "-c", "2048", "-t", "0", "128", "256"], "threads"),
+    ("hf_rocm_kernels.benchmarks.swiglu.vs_vllm", ["-r", "4", "-i", "1024"], "Ours (us)"),
+    ("hf_rocm_kernels.benchmarks.residual_rms.vs_vllm", ["-r", "4", "-c", "1024"], "Ours (us)"),
     ("hf_rocm_kernels.benchmarks.llama_mlp.block", ["--tokens", "4", "--hidden", "1024", "--intermediate", "2048"],
      "four launches"),
     ("hf_rocm_kernels.benchmarks.llama_mlp.block", ["--tokens", "4", "--hidden", "1024", "--intermediate", "2048",
