@@ -479,10 +479,12 @@ def cpu_baseline(torch, wl):
 
     picked, inputs = cpu_sample(torch, wl)
     seconds = port.time_cases(inputs, repeats=2)
+    seconds_wide = port.time_cases_predequantised(inputs, repeats=2)
     nbytes = sum(c.algorithmic_bytes() for c in picked)
     return {"value": round(nbytes / seconds / 1e12, 6), "unit": UNIT, "cores": port.host_threads(), "kind": "port",
             "sample": "the four M=16 calls of the workload once (218 MB of weights), dequantise + fp32 matmul, "
-                      "torch CPU, best of 2"}
+                      "torch CPU, best of 2",
+            "value_weights_predequantised": round(nbytes / seconds_wide / 1e12, 6)}
 
 
 def run_reference(args):

@@ -29,6 +29,28 @@ def skinny_gemm_cpu(a_q: torch.Tensor, w_q: torch.Tensor, scale: torch.Tensor, d
     return acc.to(out_dtype)
 
 
+def time_cases_predequantised(inputs: List[Dict[str, torch.Tensor]], repeats: int = 1,
+                              threads: Optional[int] = None) -> float:
+    """As :func:`time_cases` with the weights converted to float32 once, outside the timed region:
+    the matmul, the scale, the bias and the cast only. The weight matrix is then 4 bytes per
+    element in host memory, which no deployment of an fp8 model would keep; the figure separates
+    the cost of the dequantisation from the cost of the product."""
+    torch.set_num_threads(threads or host_threads())
+    wide = [inp["w"].float() for inp in inputs]
+    best = float("inf")
+    for rep in range(repeats + 1):
+        start = time.perf_counter()
+        for inp, w32 in zip(inputs, wide):
+            acc = (inp["a"].float() @ w32.t()) * inp["scale"].float()
+            if inp["d_in"] is not None:
+                acc = acc + inp["d_in"].float()
+            acc.to(torch.bfloat16)
+        elapsed = time.perf_counter() - start
+        if rep > 0:
+            best = min(best, elapsed)
+    return best
+
+
 def time_cases(inputs: List[Dict[str, torch.Tensor]], repeats: int = 1, threads: Optional[int] = None) -> float:
     """Seconds for one pass over ``inputs`` (dicts from ``workloads.make_inputs`` on CPU), best of
     ``repeats`` after one untimed pass."""
