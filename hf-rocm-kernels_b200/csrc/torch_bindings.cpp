@@ -151,6 +151,25 @@ TORCH_LIBRARY(_HFRK_C, ops) {
     ops.impl("skinny_gemm_tb", torch::kCUDA, &skinny_gemm_tb);
 }
 
+// Shape-only implementations for the Meta key, so that graph tracers (torch.compile, fake tensors)
+// can step over the ops: every op works in place on tensors the caller allocated, so there is
+// nothing to compute. The reference registers none; a serving engine that compiles its model needs them.
+int64_t skinny_gemm_tb_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, int64_t, int64_t, int64_t,
+                            int64_t, int64_t, int64_t, int64_t, int64_t, int64_t) {
+    return HFRK_SUCCESS;
+}
+void swiglu_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, int64_t, bool) {}
+void residual_rms_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, double, torch::Tensor&,
+                       torch::Tensor&, int64_t, bool) {}
+void increment_meta(torch::Tensor&) {}
+
+TORCH_LIBRARY_IMPL(_HFRK_C, Meta, ops) {
+    ops.impl("skinny_gemm_tb", &skinny_gemm_tb_meta);
+    ops.impl("swiglu", &swiglu_meta);
+    ops.impl("residual_rms", &residual_rms_meta);
+    ops.impl("increment", &increment_meta);
+}
+
 // `import hf_rocm_kernels._HFRK_C` only has to load this shared object so that the static
 // registration above runs; the module itself is empty.
 PyMODINIT_FUNC PyInit__HFRK_C(void) {

@@ -237,3 +237,22 @@ def test_the_package_fails_loudly_without_its_native_library(native_build, tmp_p
     with pytest.raises(AssertionError, match="cuda"):
         residual_rms(torch.zeros((2, 64), dtype=torch.float16), torch.zeros((2, 64), dtype=torch.float16),
                      torch.ones(64, dtype=torch.float16), 1e-5)
+
+
+def test_ops_can_be_traced_with_meta_tensors(pkg):
+    """A tracer that runs the model on meta tensors must get through the four ops (they work in
+    place on caller-allocated tensors, so the shape-only implementations do nothing)."""
+    meta = torch.device("meta")
+    a = torch.empty((4, 256), dtype=torch.float8_e4m3fn, device=meta)
+    w = torch.empty((128, 256), dtype=torch.float8_e4m3fn, device=meta)
+    d = torch.empty((4, 128), dtype=torch.bfloat16, device=meta)
+    s = torch.empty(1, device=meta)
+    assert torch.ops._HFRK_C.skinny_gemm_tb(a, w.t(), d, s, 0, 1, 1, 1, 1, 1, 12, 16, 4) == 0
+    gate_up = torch.empty((4, 64), dtype=torch.float16, device=meta)
+    out = torch.empty((4, 32), dtype=torch.float8_e4m3fnuz, device=meta)
+    buf = torch.empty((4, 0), dtype=torch.float16, device=meta)
+    assert torch.ops._HFRK_C.swiglu(gate_up, s, out, buf, 64, False) is None
+    x = torch.empty((4, 64), dtype=torch.float16, device=meta)
+    weight = torch.empty(64, dtype=torch.float16, device=meta)
+    assert torch.ops._HFRK_C.residual_rms(x, x, weight, s, 1e-5, torch.empty_like(x), buf, 0, False) is None
+    assert torch.ops._HFRK_C.increment(x) is None
