@@ -58,6 +58,14 @@ int64_t skinny_gemm_tb(torch::Tensor& A, torch::Tensor& B, torch::Tensor& D, tor
                                 /*accumulate=*/1, static_cast<int>(split_k > 16 ? 16 : split_k), stream);
 }
 
+// The same GEMM for graph tracers: an op that returns an int cannot be captured into a traced graph,
+// so this form returns nothing and raises on a non-zero status. No counterpart in the reference.
+void skinny_gemm_inplace(torch::Tensor& A, torch::Tensor& B, torch::Tensor& D, torch::Tensor& scale_tensor,
+                         int64_t split_k) {
+    const int64_t status = skinny_gemm_tb(A, B, D, scale_tensor, split_k, 1, 1, 1, 1, 1, 12, 16, 4);
+    TORCH_CHECK(status == HFRK_SUCCESS, "skinny_gemm: status ", status, " (see hfrk_b200.h)");
+}
+
 // gate_up [rows, 2*hidden] fp16/bf16 -> output [rows, hidden] fp8 (e4m3fnuz as in the reference, or
 // e4m3fn), next_buffer [rows, any] 16-bit zeroed. Stands where the reference has
 // csrc/op_src/swiglu/swiglu_dispatch.cu:8-42. num_threads belonged to the reference's launch and is
@@ -149,6 +157,8 @@ TORCH_LIBRARY(_HFRK_C, ops) {
         "skinny_gemm_tb(Tensor A, Tensor B, Tensor! D, Tensor scale_tensor, int split_k, int A_producers, "
         "int B_producers, int consumers, int a_lanes, int b_lanes, int qsize, int op_m, int ops) -> int");
     ops.impl("skinny_gemm_tb", torch::kCUDA, &skinny_gemm_tb);
+    ops.def("skinny_gemm_inplace(Tensor A, Tensor B, Tensor! D, Tensor scale_tensor, int split_k) -> ()");
+    ops.impl("skinny_gemm_inplace", torch::kCUDA, &skinny_gemm_inplace);
 }
 
 // Shape-only implementations for the Meta key, so that graph tracers (torch.compile, fake tensors)
@@ -158,6 +168,7 @@ int64_t skinny_gemm_tb_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torc
                             int64_t, int64_t, int64_t, int64_t, int64_t, int64_t) {
     return HFRK_SUCCESS;
 }
+void skinny_gemm_inplace_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, int64_t) {}
 void swiglu_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, int64_t, bool) {}
 void residual_rms_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, double, torch::Tensor&,
                        torch::Tensor&, int64_t, bool) {}
@@ -165,6 +176,7 @@ void increment_meta(torch::Tensor&) {}
 
 TORCH_LIBRARY_IMPL(_HFRK_C, Meta, ops) {
     ops.impl("skinny_gemm_tb", &skinny_gemm_tb_meta);
+    ops.impl("skinny_gemm_inplace", &skinny_gemm_inplace_meta);
     ops.impl("swiglu", &swiglu_meta);
     ops.impl("residual_rms", &residual_rms_meta);
     ops.impl("increment", &increment_meta);

@@ -95,6 +95,10 @@ def skinny_gemm(
     if output is None:
         output = torch.zeros((skinny_a.size(0), b.size(1)), dtype=torch.float16, device=skinny_a.device)
     skinny_gemm_checks(skinny_a, b, scale_tensor, output)
+    if torch.compiler.is_compiling():
+        # a traced graph cannot hold an op that returns an int: same kernel, raises on a bad status
+        torch.ops._HFRK_C.skinny_gemm_inplace(skinny_a, b, output, scale_tensor, 0)
+        return output
     status = _skinny_gemm(A=skinny_a, B=b, scale_tensor=scale_tensor, D=output, **infer_skinny_gemm_params(skinny_a, b))
     if status != 0:
         raise RuntimeError(f"skinny_gemm failed with status {status}: {_STATUS_TEXT.get(status, 'see hfrk_b200.h')}")
