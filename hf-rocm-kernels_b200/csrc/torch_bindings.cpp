@@ -66,6 +66,36 @@ void skinny_gemm_inplace(torch::Tensor& A, torch::Tensor& B, torch::Tensor& D, t
     TORCH_CHECK(status == HFRK_SUCCESS, "skinny_gemm: status ", status, " (see hfrk_b200.h)");
 }
 
+// Gate/up projection with swiglu in its epilogue (hfrk_skinny_gemm_fp8_swiglu): A [m, k] fp8, B the
+// [k, 2*inter] view (stride(0) == 1) of the row-major gate/up weight, act_out [m, inter] fp8,
+// next_buffer [m, any] 16-bit zeroed. mid_bf16 names the 16-bit type the unfused chain would have
+// stored the projection in. No counterpart in the reference.
+void skinny_gemm_swiglu(torch::Tensor& A, torch::Tensor& B, torch::Tensor& act_out, torch::Tensor& scale_tensor,
+                        torch::Tensor& act_scale_tensor, torch::Tensor& next_buffer, bool mid_bf16) {
+    TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && B.stride(0) == 1 && A.is_contiguous() && act_out.is_contiguous() &&
+                    A.size(1) == B.size(0) && B.size(1) % 2 == 0 && act_out.numel() == A.size(0) * (B.size(1) / 2),
+                "skinny_gemm_swiglu: expected A [m, k], B [k, 2*inter] column-major, act_out [m, inter]");
+    TORCH_CHECK(scale_tensor.numel() == 1 && act_scale_tensor.numel() == 1 &&
+                    scale_tensor.scalar_type() == at::ScalarType::Float &&
+                    act_scale_tensor.scalar_type() == at::ScalarType::Float,
+                "skinny_gemm_swiglu: the two scales must hold one fp32 each");
+    const int a_kind = fp8_kind_of(A), w_kind = fp8_kind_of(B), out_kind = fp8_kind_of(act_out);
+    TORCH_CHECK(a_kind >= 0 && w_kind >= 0 && out_kind >= 0, "skinny_gemm_swiglu: A, B and act_out must be e4m3");
+    const int64_t m = A.size(0), k = A.size(1), inter = B.size(1) / 2;
+    TORCH_CHECK(next_buffer.is_contiguous() && next_buffer.element_size() == 2 &&
+                    (next_buffer.numel() == 0 || next_buffer.size(0) == m),
+                "skinny_gemm_swiglu: next_buffer must be a contiguous 16-bit [m, .] matrix");
+    TORCH_CHECK(m <= INT32_MAX && inter <= INT32_MAX && k <= INT32_MAX, "skinny_gemm_swiglu: extent above 2^31");
+    const at::cuda::OptionalCUDAGuard device_guard(device_of(A));
+    const cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    const int status = hfrk_skinny_gemm_fp8_swiglu(
+        A.data_ptr(), B.data_ptr(), act_out.data_ptr(), static_cast<const float*>(scale_tensor.data_ptr()),
+        static_cast<const float*>(act_scale_tensor.data_ptr()), next_buffer.data_ptr(), static_cast<int>(m),
+        static_cast<int>(inter), static_cast<int>(k), B.stride(1), a_kind, w_kind, mid_bf16 ? HFRK_BF16 : HFRK_F16,
+        out_kind, m == 0 ? 0 : next_buffer.numel() / m, stream);
+    TORCH_CHECK(status == HFRK_SUCCESS, "skinny_gemm_swiglu: status ", status, " (", hfrk_last_error(), ")");
+}
+
 // gate_up [rows, 2*hidden] fp16/bf16 -> output [rows, hidden] fp8 (e4m3fnuz as in the reference, or
 // e4m3fn), next_buffer [rows, any] 16-bit zeroed. Stands where the reference has
 // csrc/op_src/swiglu/swiglu_dispatch.cu:8-42. num_threads belonged to the reference's launch and is
@@ -159,6 +189,10 @@ TORCH_LIBRARY(_HFRK_C, ops) {
     ops.impl("skinny_gemm_tb", torch::kCUDA, &skinny_gemm_tb);
     ops.def("skinny_gemm_inplace(Tensor A, Tensor B, Tensor! D, Tensor scale_tensor, int split_k) -> ()");
     ops.impl("skinny_gemm_inplace", torch::kCUDA, &skinny_gemm_inplace);
+    ops.def(
+        "skinny_gemm_swiglu(Tensor A, Tensor B, Tensor! act_out, Tensor scale_tensor, Tensor act_scale_tensor, "
+        "Tensor! next_buffer, bool mid_bf16) -> ()");
+    ops.impl("skinny_gemm_swiglu", torch::kCUDA, &skinny_gemm_swiglu);
 }
 
 // Shape-only implementations for the Meta key, so that graph tracers (torch.compile, fake tensors)
@@ -169,6 +203,8 @@ int64_t skinny_gemm_tb_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torc
     return HFRK_SUCCESS;
 }
 void skinny_gemm_inplace_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, int64_t) {}
+void skinny_gemm_swiglu_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&,
+                             torch::Tensor&, bool) {}
 void swiglu_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, int64_t, bool) {}
 void residual_rms_meta(torch::Tensor&, torch::Tensor&, torch::Tensor&, torch::Tensor&, double, torch::Tensor&,
                        torch::Tensor&, int64_t, bool) {}
@@ -177,6 +213,7 @@ void increment_meta(torch::Tensor&) {}
 TORCH_LIBRARY_IMPL(_HFRK_C, Meta, ops) {
     ops.impl("skinny_gemm_tb", &skinny_gemm_tb_meta);
     ops.impl("skinny_gemm_inplace", &skinny_gemm_inplace_meta);
+    ops.impl("skinny_gemm_swiglu", &skinny_gemm_swiglu_meta);
     ops.impl("swiglu", &swiglu_meta);
     ops.impl("residual_rms", &residual_rms_meta);
     ops.impl("increment", &increment_meta);

@@ -18,7 +18,8 @@ from typing import Optional, Tuple
 import torch
 from torch import Tensor
 
-from hf_rocm_kernels import _capi, residual_rms, skinny_gemm, swiglu
+import hf_rocm_kernels._HFRK_C  # noqa: F401  (registers torch.ops._HFRK_C)
+from hf_rocm_kernels import residual_rms, skinny_gemm, swiglu
 from hf_rocm_kernels.combined_ops.row_parallel import RowParallelSkinnyGemm
 
 
@@ -43,12 +44,15 @@ def skinny_gemm_swiglu(
     ``swiglu``. ``gate_up_weight`` is the (hidden, 2 * intermediate) column-major view, gate columns
     first; ``next_buffer`` (16-bit, tokens rows) is zeroed."""
     assert gate_up_weight.dim() == 2 and gate_up_weight.stride(0) == 1, "expected the column-major [K, N] view"
+    assert mid_dtype in (torch.float16, torch.bfloat16), f"Expected a 16-bit mid_dtype but got {mid_dtype}"
     tokens, inter = skinny_a.size(0), gate_up_weight.size(1) // 2
+    if tokens > 16:
+        raise RuntimeError("skinny_gemm_swiglu takes at most 16 tokens; run skinny_gemm and swiglu instead")
     out = torch.empty((tokens, inter), dtype=out_dtype or gate_up_weight.dtype, device=skinny_a.device)
-    status = _capi.skinny_gemm_swiglu(skinny_a, gate_up_weight.t(), out, scale_tensor, act_scale_tensor, next_buffer,
-                                      mid_dtype)
-    if status != 0:
-        raise RuntimeError(f"skinny_gemm_swiglu failed with status {status} ({_capi.STATUS_NAMES.get(status, '?')})")
+    if next_buffer is None:
+        next_buffer = torch.empty((tokens, 0), dtype=mid_dtype, device=skinny_a.device)
+    torch.ops._HFRK_C.skinny_gemm_swiglu(skinny_a, gate_up_weight, out, scale_tensor, act_scale_tensor, next_buffer,
+                                         mid_dtype == torch.bfloat16)
     return out
 
 

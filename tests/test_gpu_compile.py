@@ -37,3 +37,29 @@ def test_the_python_api_compiles_without_graph_breaks(native_build):
         got = compiled(a_q, scale)
         torch.cuda.synchronize()
         assert all(torch.equal(as_bytes(g), as_bytes(e)) for g, e in zip(got, eager))
+
+
+def test_the_mlp_block_compiles_without_graph_breaks(native_build):
+    from hf_rocm_kernels.combined_ops import llama_mlp_combined_ops
+    from hf_rocm_kernels.utils.fp8 import fp8_quantize_e4m3fn
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(6)
+    tokens, hidden, inter = 8, 1024, 2048
+    attn = torch.randn(tokens, hidden, device=dev).bfloat16()
+    residual = torch.randn(tokens, hidden, device=dev).bfloat16()
+    gamma = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
+    w_gu, s_gu = fp8_quantize_e4m3fn(torch.randn(2 * inter, hidden, device=dev) * 0.02)
+    w_dn, s_dn = fp8_quantize_e4m3fn(torch.randn(hidden, inter, device=dev) * 0.02)
+    s_in = torch.tensor([4.0 / 448], device=dev)
+    s_act = torch.tensor([16.0 / 448], device=dev)
+
+    def block(attn, residual):
+        return llama_mlp_combined_ops(attn, residual, gamma, 1e-5, w_gu.t(), s_in, s_in * s_gu, w_dn.t(), s_act,
+                                      s_act * s_dn)
+
+    want_out, want_res = block(attn, residual.clone())
+    compiled = torch.compile(block, backend="aot_eager", fullgraph=True)
+    got_out, got_res = compiled(attn, residual.clone())
+    torch.cuda.synchronize()
+    assert torch.equal(got_out, want_out) and torch.equal(got_res, want_res)
