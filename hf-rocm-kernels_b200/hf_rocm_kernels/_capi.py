@@ -145,6 +145,24 @@ def _common_args(a: torch.Tensor, w: torch.Tensor, d: torch.Tensor, scale: torch
             fp8_kind(a.dtype), fp8_kind(w.dtype), out_kind(d.dtype), int(accumulate))
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on_device(device: torch.device):
+    """Context that makes ``device`` current; free when it already is (the usual case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _stream_ptr(stream: Optional[torch.cuda.Stream], device: torch.device) -> int:
     return (stream or torch.cuda.current_stream(device)).cuda_stream
 
@@ -196,7 +214,7 @@ def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True
     assert a_host.device.type == "cpu" and d_host.device.type == "cpu" and w_dev.stride(1) == 1
     assert work_dev.numel() * work_dev.element_size() >= lib.hfrk_host_call_workspace_bytes(m, n, k)
     entry = lib.hfrk_skinny_gemm_fp8_host if synchronise else lib.hfrk_skinny_gemm_fp8_host_async
-    with torch.cuda.device(w_dev.device):
+    with _on_device(w_dev.device):
         return entry(
             a_host.data_ptr(), w_dev.data_ptr(), d_host.data_ptr(), scale_dev.data_ptr(), m, n, k, w_dev.stride(0),
             fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype), out_kind(d_host.dtype), int(accumulate),
