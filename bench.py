@@ -336,7 +336,7 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": int(step_bytes / len(items)), "peak_source": peak_source,
                          "kernel": "skinny_gemm_fp8_sm100_kernel", "launches": args.steps * len(items)},
             "e2e": {"value": round(e2e_value, 4), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "note": "host activations/bias in, host result out, every call; weights resident; a step queues its calls on two streams and waits once"},
+                    "steps": e2e_steps, "note": "host activations/bias in, host result out, every call; weights resident; activations by copy, bias and result read and written by the kernel in page-locked host memory; a step queues its calls on two streams and waits once"},
             "gpu_launches": args.steps * len(items),
             "clocks": clocks,
         }

@@ -102,8 +102,9 @@ int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* 
                             void* stream);
 
 /* Host-buffer form of the same call, for callers whose activations live in host memory:
- * copies A (and D when accumulate=1) host->device, runs the GEMM against the device-resident
- * weights W_dev, copies D back, and synchronises `stream`. `work_dev` is caller-owned device
+ * copies A host->device, runs the GEMM against the device-resident weights W_dev with D in host
+ * memory, and synchronises `stream`. When D_host is page-locked the kernel reads (accumulate=1)
+ * and writes it directly over PCIe; pageable memory is staged through `work_dev` with copies. `work_dev` is caller-owned device
  * scratch of at least hfrk_host_call_workspace_bytes(m, n, k) bytes. Weights stay on the
  * device: they are model state, as in the reference where they are torch CUDA tensors
  * (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:28-35). */

@@ -326,6 +326,12 @@ def test_host_buffer_entry_point(capi, dev, checker):
         stream.synchronize()
     assert all(torch.equal(out, d_host) for out in outs)
 
+    # pageable host memory takes the staged route (copies through the workspace): same bytes
+    pageable = inp["d_in"].clone()
+    assert not pageable.is_pinned()
+    capi.check(capi.skinny_gemm_host(inp["a"].clone(), w, pageable, s, work))
+    assert torch.equal(pageable, d_host)
+
 
 def test_profile_entry_point_records_ordered_stamps(capi, dev):
     a = torch.randint(0, 120, (16, 4096), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
