@@ -66,11 +66,12 @@ enum hfrk_out_dtype { HFRK_F16 = 0, HFRK_BF16 = 1, HFRK_F32 = 2 };
 enum hfrk_variant { HFRK_VARIANT_AUTO = 0, HFRK_VARIANT_CLUSTER = 1, HFRK_VARIANT_STREAMK = 2 };
 
 /* Single-GPU skinny GEMM on `stream` (a cudaStream_t passed as void*), asynchronous, no host
- * synchronisation. The first call on a device allocates the library's scratch memory (about
- * 80 MB, kept until the process ends), so it must come before any stream capture; later calls
- * allocate nothing and can be captured in a CUDA graph. Calls on up to four streams of a device
- * may overlap; beyond four distinct streams two of them share scratch and must not run GEMMs at
- * the same time.
+ * synchronisation. The kernel this entry point launches (the cluster kernel) needs no scratch and
+ * the call allocates no device memory; the first call on a device sets the kernels' attributes,
+ * so make one call per device before capturing into a CUDA graph. Only the stream-K variant
+ * (hfrk_skinny_gemm_fp8_ex with HFRK_VARIANT_STREAMK) owns scratch: about 80 MB per device,
+ * allocated on its first use (before any capture) and kept until the process ends, in four lanes
+ * so that calls on up to four streams of a device may overlap.
  * Replaces skinny_gemm_tb / skinny_gemm() of the reference
  * (csrc/op_src/skinny_gemm/skinny_gemm_binding.cu:16-42, skinny_gemm_caller.cu:21-71).
  *   a_kind, w_kind : enum hfrk_fp8_kind       d_dtype : enum hfrk_out_dtype
