@@ -105,19 +105,19 @@ int hfrk_skinny_gemm_fp8_ex(const void* A, const void* W, void* D, const float* 
 /* Host-buffer form of the same call, for callers whose activations live in host memory:
  * copies A host->device, runs the GEMM against the device-resident weights W_dev with D in host
  * memory, and synchronises `stream`. When D_host is page-locked the kernel reads (accumulate=1)
- * and writes it directly over PCIe; pageable memory is staged through `work_dev` with copies. `work_dev` is caller-owned device
- * scratch of at least hfrk_host_call_workspace_bytes(m, n, k) bytes. Weights stay on the
- * device: they are model state, as in the reference where they are torch CUDA tensors
- * (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:28-35). */
+ * and writes it directly over PCIe; pageable memory is staged through `work_dev` with copies.
+ * `work_dev` is caller-owned device scratch of at least hfrk_host_call_workspace_bytes(m, n, k)
+ * bytes. Weights stay on the device: they are model state, as in the reference where they are
+ * torch CUDA tensors (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:28-35). */
 int hfrk_skinny_gemm_fp8_host(const void* A_host, const void* W_dev, void* D_host,
                               const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
                               int a_kind, int w_kind, int d_dtype, int accumulate,
                               void* work_dev, void* stream);
 int64_t hfrk_host_call_workspace_bytes(int m, int n, int k);
-/* The same three copies and the GEMM queued on `stream` WITHOUT the final synchronisation: D_host
- * holds the result once the caller has synchronised the stream. A_host, D_host (pinned, or the
- * copies are not asynchronous) and work_dev must stay untouched until then; calls that share a
- * work_dev must share the stream. Lets a decode step queue all of its projections and wait once. */
+/* The same work queued on `stream` WITHOUT the final synchronisation: D_host holds the result once
+ * the caller has synchronised the stream. A_host, D_host (page-locked, or the copies are not
+ * asynchronous) and work_dev must stay untouched until then; calls that share a work_dev must
+ * share the stream. Lets a decode step queue all of its projections and wait once. */
 int hfrk_skinny_gemm_fp8_host_async(const void* A_host, const void* W_dev, void* D_host,
                                     const float* scale_dev, int m, int n, int k, int64_t w_row_stride,
                                     int a_kind, int w_kind, int d_dtype, int accumulate,
@@ -132,13 +132,13 @@ int hfrk_skinny_gemm_fp8_host_async(const void* A_host, const void* W_dev, void*
  * NVLink; a cell is valid once it carries the current call number, so no flag or fence is
  * needed), polls its own buffer for the peers' cells (bounded, ~2 s: HFRK_DEVICE_TIMEOUT through
  * hfrk_device_status) and adds the contributions in rank order, so all ranks produce
- * bit-identical results. One process per
- * GPU: create -> exchange the 64-byte IPC handles by any host-side all-gather -> connect.
+ * bit-identical results (hfrk_rowpar_set_mode describes the second exchange scheme). One process
+ * per GPU: create -> exchange the 64-byte IPC handles by any host-side all-gather -> connect.
  * The reference has no multi-GPU path at all (no collective call site exists in its tree); this
  * stands where the benchmark specification asks for "GEMM + allreduce" in combined_ops.
  * All ranks must issue the same sequence of calls on a group. A group serves one stream at a time.
  *   max_m, max_n : largest call the group will see (sizes the exchange buffer:
- *                  2 * world * min(max_m,16) * roundup(max_n,128) * 8 bytes). */
+ *                  2 * (world + 1) * min(max_m,16) * roundup(max_n,128) * 8 bytes). */
 typedef struct hfrk_rowpar hfrk_rowpar;
 int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out);
 int hfrk_rowpar_ipc_handle(hfrk_rowpar* group, void* handle64_out);
