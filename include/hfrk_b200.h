@@ -217,8 +217,10 @@ int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int cta
  * e4m3fnuz, where callers pass the DOUBLED scale of hf_rocm_kernels/utils/fp8.py:31-33. The
  * bytes saturate at +-224 (0x7e), as utils/fp8.py:19-20 clamps, not at the +-240 (0x7f) of the
  * HIP conversion: 0x7f is NaN to a consumer that multiplies the bytes natively as e4m3fn, as the
- * GEMM here does. Negative zero is written as 0x00 (utils/fp8.py:26-30). HFRK_OUT_E4M3FN writes
- * value / scale in e4m3fn, saturating at +-448. */
+ * GEMM here does. Negative zero is written as 0x00 (utils/fp8.py:26-30). A NaN input comes out as
+ * 0x7f/0xff, the NaN of e4m3fn, which that consumer propagates (a reader that decodes the bytes as
+ * true e4m3fnuz would see +-240 there). HFRK_OUT_E4M3FN writes value / scale in e4m3fn, saturating
+ * at +-448. */
 enum hfrk_norm_out { HFRK_OUT_SAME = 0, HFRK_OUT_E4M3FN = 1, HFRK_OUT_E4M3FNUZ = 2 };
 
 /* out[r, c] = fp8( silu(gate_up[r, c]) * gate_up[r, hidden + c] / scale ),  c < hidden;
