@@ -223,7 +223,8 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
 //   kModeRowPar : the epilogue all-reduces the tile over the ranks of a row-parallel group before D is written
 //   kModeSwiglu : W is a gate/up projection; a CTA's tile is 64 gate rows plus the matching 64 up rows,
 //                 and the epilogue writes fp8(silu(gate) * up / act_scale) instead of the projection
-//                 (split == 1 and m <= 16 only: the host guarantees both)
+//                 (m <= 16: the host guarantees it; with a K split every CTA of the cluster ends up
+//                 with whole token rows of the tile, so the two halves of a column still meet)
 constexpr int kModePlain = 0;
 constexpr int kModeRowPar = 1;
 constexpr int kModeSwiglu = 2;
