@@ -25,7 +25,7 @@ TORCH_EXT = os.path.join(PKG, "_HFRK_C.so")
 CUDA_SOURCES = ["skinny_gemm_sm100.cu", "skinny_gemm_simt.cu", "swiglu_sm100.cu", "residual_rms_sm100.cu",
                 "host_common.cu"]
 CUDA_HEADERS = ["ptx_sm100.cuh", "host_common.h", "elementwise_common.cuh", "skinny_gemm_common.cuh",
-                "skinny_gemm_kernel.cuh", "skinny_gemm_streamk.cuh",
+                "skinny_gemm_kernel.cuh", "skinny_gemm_streamk.cuh", "device_model.cuh",
                 os.path.join("..", "..", "include", "hfrk_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]

@@ -207,6 +207,30 @@ __device__ __forceinline__ void dsmem_bulk_copy(uint32_t dst_cluster_addr, uint3
         : "memory");
 }
 
+// Asynchronous stores from registers into a peer's shared memory (addresses from dsmem_map). Each
+// store adds its own size to the transaction count of the PEER's mbarrier when it has landed, so
+// the receiver learns from one barrier that every sender's data is there. No staging in shared
+// memory, no proxy fence and no copy engine on the way.
+__device__ __forceinline__ void st_async_b32(uint32_t dst_cluster_addr, uint32_t a, uint32_t peer_bar_cluster_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(dst_cluster_addr), "r"(a), "r"(peer_bar_cluster_addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_async_v2_b32(uint32_t dst_cluster_addr, uint32_t a, uint32_t b,
+                                                uint32_t peer_bar_cluster_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];"
+                 ::"r"(dst_cluster_addr), "r"(a), "r"(b), "r"(peer_bar_cluster_addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_async_v4_b32(uint32_t dst_cluster_addr, uint32_t a, uint32_t b, uint32_t c,
+                                                uint32_t d, uint32_t peer_bar_cluster_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(dst_cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(peer_bar_cluster_addr)
+                 : "memory");
+}
+
 // The issuing thread's bulk copies have finished READING their source.
 __device__ __forceinline__ void bulk_copies_source_done() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -57,6 +57,7 @@ struct GemmParams {
     int tile_rows;       // W rows per CTA, <= 128: the MMA always covers 128 lanes, the rest is ignored
     int num_kblocks;     // ceil(k / 128)
     int split;           // CTAs per cluster along K
+    int rows_log2;       // split > 1: CTA q of a cluster finishes token rows [q << rows_log2, (q + 1) << rows_log2)
     int stages;
     int d_dtype;
     int accumulate;
@@ -230,13 +231,486 @@ constexpr int kModeRowPar = 1;
 constexpr int kModeSwiglu = 2;
 constexpr int kHalfTile = kTileN / 2;
 constexpr int kAutoTileRowsOff = -1;   // make_plan: keep 128-row tiles (callers whose layout depends on them)
+constexpr int kEpiPitch = kTileN + 4;  // floats per token row of the transposed tile staged in shared memory
+constexpr int kOwned = 8;              // token rows per owner kept in registers in the split-K reduction
 
 __device__ __forceinline__ float round_trip_16(float x, int dtype) {
     return dtype == HFRK_BF16 ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
 }
 
+// ---------------------------------------------------------------- output accessors, one per D type
+// The epilogue is compiled once per output type: every warp of it runs alone on its scheduler, so
+// its time is its instruction count, and a type switch per element doubled that count.
+template <int DT>
+__device__ __forceinline__ float load1(const void* d, size_t idx) {
+    if constexpr (DT == HFRK_F32) return static_cast<const float*>(d)[idx];
+    if constexpr (DT == HFRK_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(d)[idx]);
+    return __half2float(static_cast<const __half*>(d)[idx]);
+}
+
+template <int DT>
+__device__ __forceinline__ void store1(void* d, size_t idx, float v) {
+    if constexpr (DT == HFRK_F32) {
+        static_cast<float*>(d)[idx] = v;
+    } else if constexpr (DT == HFRK_BF16) {
+        static_cast<__nv_bfloat16*>(d)[idx] = __float2bfloat16_rn(v);
+    } else {
+        static_cast<__half*>(d)[idx] = __float2half_rn(v);
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ constexpr int out_bytes() { return DT == HFRK_F32 ? 4 : 2; }
+
+// Sixteen consecutive outputs as raw 16-byte words (two for the 16-bit types, four for float).
+template <int DT>
+struct Raw16 {
+    uint4 q[DT == HFRK_F32 ? 4 : 2];
+};
+
+template <int DT>
+__device__ __forceinline__ Raw16<DT> load_raw16(const void* d, size_t idx) {
+    Raw16<DT> r;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(d) + idx * out_bytes<DT>());
+#pragma unroll
+    for (int i = 0; i < (DT == HFRK_F32 ? 4 : 2); ++i) r.q[i] = src[i];
+    return r;
+}
+
+template <int DT>
+__device__ __forceinline__ void decode16(const Raw16<DT>& r, float (&x)[16]) {
+    if constexpr (DT == HFRK_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[4 * i] = __uint_as_float(r.q[i].x);
+            x[4 * i + 1] = __uint_as_float(r.q[i].y);
+            x[4 * i + 2] = __uint_as_float(r.q[i].z);
+            x[4 * i + 3] = __uint_as_float(r.q[i].w);
+        }
+    } else {
+        const uint32_t w[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float2 f;
+            if constexpr (DT == HFRK_BF16) {
+                f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            } else {
+                f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            }
+            x[2 * i] = f.x;
+            x[2 * i + 1] = f.y;
+        }
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void store16(void* d, size_t idx, const float (&y)[16]) {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(d) + idx * out_bytes<DT>());
+    if constexpr (DT == HFRK_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            dst[i] = make_uint4(__float_as_uint(y[4 * i]), __float_as_uint(y[4 * i + 1]), __float_as_uint(y[4 * i + 2]),
+                                __float_as_uint(y[4 * i + 3]));
+        }
+    } else {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if constexpr (DT == HFRK_BF16) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                const __half2 h = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+
+// What the epilogue functions share.
+struct EpiCtx {
+    Ctrl* ctrl;
+    uint8_t* ring_ptr;      // start of the (by then idle) stage ring
+    uint32_t recv_addr;     // shared-memory address of float recv[split][128][rpo]
+    uint32_t recv_bar;
+    uint32_t accum_bar;
+    uint32_t lane_taddr;    // TMEM address of this thread's lane, column 0
+    int rank;               // CTA rank in the cluster (0 without a K split)
+    int n0;                 // first W row of the tile
+    float scale;
+};
+
+// Sends 16 token rows (c0 .. c0 + 15) of this thread's W row to the CTAs that finish them. Token
+// row r goes to CTA r >> rows_log2, position r & (rpo - 1) of this thread's slot there. Rows leave
+// 1, 2 or 4 at a time (min(rpo, 4)); a group never straddles two owners because its size divides
+// rpo. An owner expects whole blocks, so the rows of its range past m are sent as they are.
+__device__ __forceinline__ void send_partial_rows(const GemmParams& p, const EpiCtx& cx, int c0, const uint32_t (&v)[16]) {
+    const int rpo = 1 << p.rows_log2;
+    const uint32_t send_base = cx.recv_addr + (static_cast<uint32_t>(cx.rank) * kTileN + threadIdx.x) * (4u << p.rows_log2);
+    if (rpo >= 4) {
+#pragma unroll
+        for (int g = 0; g < 16; g += 4) {
+            const int r0 = c0 + g;
+            const uint32_t q = static_cast<uint32_t>(r0 >> p.rows_log2);
+            if (static_cast<int>(q << p.rows_log2) < p.m) {
+                st_async_v4_b32(dsmem_map(send_base + 4u * (r0 & (rpo - 1)), q), v[g], v[g + 1], v[g + 2], v[g + 3],
+                                dsmem_map(cx.recv_bar, q));
+            }
+        }
+    } else if (rpo == 2) {
+#pragma unroll
+        for (int g = 0; g < 16; g += 2) {
+            const int r = c0 + g;
+            if (r < p.m) {
+                const uint32_t q = static_cast<uint32_t>(r >> 1);
+                st_async_v2_b32(dsmem_map(send_base, q), v[g], v[g + 1], dsmem_map(cx.recv_bar, q));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int g = 0; g < 16; ++g) {
+            const int r = c0 + g;
+            if (r < p.m) {
+                st_async_b32(dsmem_map(send_base, static_cast<uint32_t>(r)), v[g], dsmem_map(cx.recv_bar, static_cast<uint32_t>(r)));
+            }
+        }
+    }
+}
+
+// Waits (bounded) for the accumulator; with a K split also for the start-up cluster barrier, after
+// which the peers' receive barriers are known to exist and to be armed. False if the CTA gave up.
+__device__ __forceinline__ bool wait_accumulator(const GemmParams& p, const EpiCtx& cx) {
+    bool ok = mbar_wait_bounded(cx.accum_bar, 0u, &cx.ctrl->abort, kRoleEpilogue);
+    ok = __all_sync(0xffffffffu, ok) && cx.ctrl->abort == 0u;
+    ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 0) stamp(p, 5);
+    tcgen05_fence_after_sync();
+    if (p.split > 1) cluster_wait_acquire();
+    return ok;
+}
+
+// Epilogue of the plain and the row-parallel kernel for output type DT, run by the 128 epilogue
+// threads. Thread t holds TMEM lane t = W row n0 + t of the tile, 16 token rows per TMEM load.
+//
+// Without a K split the tile is turned in shared memory (the idle ring) so that the stores run
+// along D's rows: work item (token row, 16 consecutive outputs) -> one thread, 32-byte loads of
+// D_in and 32-byte stores; with 16 tokens that is exactly one item per thread, whose D_in is
+// requested before the accumulator is waited for. Ragged or unaligned items fall back to
+// element-wise accesses.
+//
+// With a K split every CTA sends its partial rows to their owners (send_partial_rows), an owner
+// waits for all `split` blocks and thread t adds up and stores column t of the owner's rows.
+template <int kMode, int DT>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx& cx) {
+    constexpr bool kRowPar = kMode == kModeRowPar;
+    const int tid = threadIdx.x;
+    const int n = cx.n0 + tid;
+    const bool direct = p.split == 1;
+    const int lim_cols = min(p.tile_rows, p.n - cx.n0);          // outputs of this tile that exist
+    const bool lane_valid = tid < lim_cols;
+    const int rpo = 1 << p.rows_log2;
+    unsigned int epoch = 0;
+    if (kRowPar) epoch = *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
+    const uint32_t tile_slot0 = blockIdx.x * static_cast<uint32_t>(p.m * kTileN);
+
+    // D_in of this thread's first work item, requested long before it is needed.
+    const int item_row = tid >> 3, item_col = (tid & 7) * 16;
+    const size_t item_idx = static_cast<size_t>(item_row) * p.n + cx.n0 + item_col;
+    const bool item_vec = direct && item_row < p.m && item_col + 16 <= lim_cols &&
+                          ((reinterpret_cast<uintptr_t>(p.d) + item_idx * out_bytes<DT>()) & 15u) == 0;
+    Raw16<DT> din_raw;
+#pragma unroll
+    for (int i = 0; i < (DT == HFRK_F32 ? 4 : 2); ++i) din_raw.q[i] = make_uint4(0, 0, 0, 0);
+    if (item_vec && p.accumulate) din_raw = load_raw16<DT>(p.d, item_idx);
+    const int own_row0 = cx.rank << p.rows_log2;                  // first token row this CTA finishes (split > 1)
+    float d_own[kOwned];
+#pragma unroll
+    for (int it = 0; it < kOwned; ++it) {
+        const int row = own_row0 + it;
+        d_own[it] = (!direct && p.accumulate && it < rpo && row < p.m && lane_valid)
+                        ? load1<DT>(p.d, static_cast<size_t>(row) * p.n + n)
+                        : 0.0f;
+    }
+
+    bool ok = wait_accumulator(p, cx);
+    float* const tile = reinterpret_cast<float*>(cx.ring_ptr);   // [m_pad][kEpiPitch], direct path only
+    if (ok) {
+        for (int c = 0; c < p.m_pad; c += 16) {
+            uint32_t v[16];
+            tmem_ld_32x32b_x16(cx.lane_taddr + static_cast<uint32_t>(c), v);
+            tmem_ld_wait();
+            if (!direct) {
+                send_partial_rows(p, cx, c, v);
+                continue;
+            }
+            if (kRowPar) {
+                // host guarantees m <= 16 here: one load, 16 values per thread
+                float val[16];
+                uint32_t slot[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    val[j] = __uint_as_float(v[j]);
+                    slot[j] = j < p.m ? tile_slot0 + static_cast<uint32_t>(j * kTileN + tid) : 0xffffffffu;
+                }
+                if (!rowpar_exchange<16>(p.rp, epoch, slot, val, &cx.ctrl->abort)) ok = false;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(val[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) tile[(c + j) * kEpiPitch + tid] = __uint_as_float(v[j]);
+        }
+    }
+    if (direct) {
+        // every thread reaches the barrier, also after a wait that ran out (then nothing is stored)
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+        if (!ok || cx.ctrl->abort != 0u) return;
+        const int items = p.m * 8;
+        for (int item = tid; item < items; item += kEpilogueThreads) {
+            const int row = item >> 3;
+            if (item_col >= lim_cols) break;                     // same column group in every pass
+            const float4* src = reinterpret_cast<const float4*>(tile + row * kEpiPitch + item_col);
+            float x[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 f = src[i];
+                x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+            }
+            const size_t idx = static_cast<size_t>(row) * p.n + cx.n0 + item_col;
+            const bool vec = item_col + 16 <= lim_cols &&
+                             ((reinterpret_cast<uintptr_t>(p.d) + idx * out_bytes<DT>()) & 15u) == 0;
+            if (vec) {
+                float y[16];
+                if (p.accumulate) {
+                    if (item == tid) {
+                        decode16<DT>(din_raw, y);
+                    } else {
+                        decode16<DT>(load_raw16<DT>(p.d, idx), y);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) y[j] = fmaf(x[j], cx.scale, y[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) y[j] = x[j] * cx.scale;
+                }
+                store16<DT>(p.d, idx, y);
+            } else {
+#pragma unroll 1
+                for (int j = 0; j < 16; ++j) {
+                    if (item_col + j < lim_cols) {
+                        const float d0 = p.accumulate ? load1<DT>(p.d, idx + j) : 0.0f;
+                        store1<DT>(p.d, idx + j, fmaf(tile[row * kEpiPitch + item_col + j], cx.scale, d0));
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    const bool owner = own_row0 < p.m;
+    bool landed = ok && (!owner || mbar_wait_bounded(cx.recv_bar, 0u, &cx.ctrl->abort, kRoleEpilogue));
+    landed = __all_sync(0xffffffffu, landed);
+    if (!landed || !owner) return;
+    const float* const mine = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(cx.ctrl) + kCtrlBytes) +
+                              (static_cast<size_t>(tid) << p.rows_log2);   // [sender] at a stride of 128 * rpo
+    const int sender_stride = kTileN << p.rows_log2;
+    float own[kOwned];
+#pragma unroll
+    for (int it = 0; it < kOwned; ++it) own[it] = 0.0f;
+    // rank order; each sender's rows for this thread are rpo consecutive floats
+    if (rpo == 1) {
+#pragma unroll 4
+        for (int q = 0; q < p.split; ++q) own[0] += mine[q * sender_stride];
+    } else if (rpo == 2) {
+#pragma unroll 4
+        for (int q = 0; q < p.split; ++q) {
+            const float2 f = *reinterpret_cast<const float2*>(mine + q * sender_stride);
+            own[0] += f.x; own[1] += f.y;
+        }
+    } else {
+#pragma unroll 2
+        for (int q = 0; q < p.split; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(mine + q * sender_stride);
+            own[0] += f.x; own[1] += f.y; own[2] += f.z; own[3] += f.w;
+            if (rpo >= 8) {
+                const float4 g = *reinterpret_cast<const float4*>(mine + q * sender_stride + 4);
+                own[4] += g.x; own[5] += g.y; own[6] += g.z; own[7] += g.w;
+            }
+        }
+    }
+    if (kRowPar) {
+        uint32_t slot[kOwned];
+#pragma unroll
+        for (int it = 0; it < kOwned; ++it) {
+            const int row = own_row0 + it;
+            slot[it] = (it < rpo && row < p.m) ? tile_slot0 + static_cast<uint32_t>(row * kTileN + tid) : 0xffffffffu;
+        }
+        if (!rowpar_exchange<kOwned>(p.rp, epoch, slot, own, &cx.ctrl->abort)) return;
+    }
+    if (!lane_valid) return;
+    {
+        const int rows = min(min(rpo, kOwned), p.m - own_row0);
+        size_t idx = static_cast<size_t>(own_row0) * p.n + n;
+#pragma unroll
+        for (int it = 0; it < kOwned; ++it) {
+            if (it < rows) store1<DT>(p.d, idx, fmaf(own[it], cx.scale, d_own[it]));
+            idx += p.n;
+        }
+    }
+    // more than 16 tokens with a small split: an owner finishes more than kOwned rows
+    for (int it = kOwned; it < rpo; ++it) {
+        const int row = own_row0 + it;
+        if (row >= p.m) break;
+        float sum = 0.0f;
+        for (int q = 0; q < p.split; ++q) sum += mine[q * sender_stride + it];
+        const size_t idx = static_cast<size_t>(row) * p.n + n;
+        const float d0 = p.accumulate ? load1<DT>(p.d, idx) : 0.0f;
+        store1<DT>(p.d, idx, fmaf(sum, cx.scale, d0));
+    }
+}
+
+// Epilogue of the gate/up kernel: fp8(silu(gate) * up / act_scale) instead of the projection, then
+// the grid zeroes the down projection's accumulate buffer.
+__device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const EpiCtx& cx) {
+    const int tid = threadIdx.x;
+    const bool direct = p.split == 1;
+    const bool ok = wait_accumulator(p, cx);
+    float* const partial = reinterpret_cast<float*>(cx.ring_ptr);  // the ring is idle by now
+    if (direct) {
+        // Lanes 0..63 hold gate columns, lanes 64..127 the matching up columns. The projection is
+        // rounded to the 16-bit type first, as the unfused chain stores it, so both give the same
+        // bytes. The activation is shared out by tokens: the gate thread of a column takes tokens
+        // 0..7, the up thread tokens 8..15, and each hands the other the eight values it needs.
+        constexpr int kPitch = 9;                        // floats per column: no bank conflicts
+        float* const handed = partial;                   // [2][64][9]: up for tokens 0..7, gate for 8..15
+        uint8_t* const out_tile = reinterpret_cast<uint8_t*>(partial + 2 * kHalfTile * kPitch);  // [16][64]
+        const int col_in_tile = tid & (kHalfTile - 1);
+        const int half = tid >> 6;                        // 0: this lane holds gate values, 1: up values
+        float y[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) y[j] = 0.0f;
+        if (ok) {
+            uint32_t v[16];
+            tmem_ld_32x32b_x16(cx.lane_taddr, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) y[j] = round_trip_16(__uint_as_float(v[j]) * cx.scale, p.d_dtype);
+        }
+        {
+            // a gate lane gives away tokens 8..15, an up lane tokens 0..7
+            float* const dst = handed + ((1 - half) * kHalfTile + col_in_tile) * kPitch;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = half == 0 ? y[8 + j] : y[j];
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+        {
+            const float inv_act = 1.0f / __ldg(p.act_scale);
+            const float* const src = handed + (half * kHalfTile + col_in_tile) * kPitch;
+            const int token0 = half * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (token0 + j < p.m) {
+                    const float gate = half == 0 ? y[j] : src[j];
+                    const float up = half == 0 ? src[j] : y[8 + j];
+                    float t = (gate / (1.0f + expf(-gate))) * up * inv_act;
+                    if (p.act_fnuz) t *= 2.0f;
+                    uint8_t byte = static_cast<uint8_t>(pack_e4m3x2(t, 0.0f) & 0xffu);
+                    if (p.act_fnuz && byte == 0x80u) byte = 0;
+                    out_tile[(token0 + j) * kHalfTile + col_in_tile] = byte;
+                }
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+        if (tid < kHalfTile && ok) {
+            const int token = tid >> 2, piece = tid & 3;
+            const int col = static_cast<int>(blockIdx.x) * kHalfTile + piece * 16;
+            if (token < p.m && col < p.act_cols) {   // act_cols % 16 == 0: a piece is inside or outside
+                *reinterpret_cast<uint4*>(p.act_out + static_cast<size_t>(token) * p.act_cols + col) =
+                    *reinterpret_cast<const uint4*>(out_tile + token * kHalfTile + piece * 16);
+            }
+        }
+    } else {
+        if (ok) {
+            uint32_t v[16];
+            tmem_ld_32x32b_x16(cx.lane_taddr, v);
+            tmem_ld_wait();
+            send_partial_rows(p, cx, 0, v);
+        }
+        const bool owner = (cx.rank << p.rows_log2) < p.m;
+        bool landed = ok && (!owner || mbar_wait_bounded(cx.recv_bar, 0u, &cx.ctrl->abort, kRoleEpilogue));
+        landed = __all_sync(0xffffffffu, landed);
+        // This CTA owns `rows` whole token rows of the tile, starting at token t0; thread
+        // tid holds lane tid of each. Same activation as in the unsplit case: the gate lane
+        // of a column takes the first half of the tokens, the up lane the second half.
+        const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(cx.ctrl) + kCtrlBytes);
+        const int per_owner = 1 << p.rows_log2;                                      // <= 8 for m <= 16, split >= 2
+        const int t0 = cx.rank << p.rows_log2;
+        const int rows = landed ? (p.m - t0 < per_owner ? p.m - t0 : per_owner) : 0;   // may be <= 0
+        const int first_half = (per_owner + 1) / 2;
+        constexpr int kPitch = 5;                                        // floats per column and half
+        float* const handed = partial;                                   // the idle ring
+        uint8_t* const out_tile = reinterpret_cast<uint8_t*>(handed + 2 * kHalfTile * kPitch);  // [8][64]
+        const int col_in_tile = tid & (kHalfTile - 1);
+        const int half = tid >> 6;
+        float y[kOwned];
+#pragma unroll
+        for (int it = 0; it < kOwned; ++it) {
+            float sum = 0.0f;
+            if (it < rows) {
+                for (int q = 0; q < p.split; ++q) sum += recv[((q * kTileN + tid) << p.rows_log2) + it];
+        }
+            y[it] = round_trip_16(sum * cx.scale, p.d_dtype);
+        }
+#pragma unroll
+        for (int it = 0; it < kOwned; ++it) {
+            const bool give = half == 0 ? it >= first_half : it < first_half;
+            if (give && it < per_owner) {
+                const int slot_in_half = half == 0 ? it - first_half : it;
+                handed[((1 - half) * kHalfTile + col_in_tile) * kPitch + slot_in_half] = y[it];
+        }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+        const float inv_act = 1.0f / __ldg(p.act_scale);
+#pragma unroll
+        for (int it = 0; it < kOwned; ++it) {
+            const bool mine = half == 0 ? it < first_half : it >= first_half;
+            if (mine && it < rows) {
+                const int slot_in_half = half == 0 ? it : it - first_half;
+                const float other = handed[(half * kHalfTile + col_in_tile) * kPitch + slot_in_half];
+                const float gate = half == 0 ? y[it] : other;
+                const float up = half == 0 ? other : y[it];
+                float t = (gate / (1.0f + expf(-gate))) * up * inv_act;
+                if (p.act_fnuz) t *= 2.0f;
+                uint8_t byte = static_cast<uint8_t>(pack_e4m3x2(t, 0.0f) & 0xffu);
+                if (p.act_fnuz && byte == 0x80u) byte = 0;
+                out_tile[it * kHalfTile + col_in_tile] = byte;
+        }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
+        if (tid < 4 * rows) {
+            const int row = tid >> 2, piece = tid & 3;
+            const int col = static_cast<int>(blockIdx.x) * kHalfTile + piece * 16;
+            if (col < p.act_cols) {
+                *reinterpret_cast<uint4*>(p.act_out + static_cast<size_t>(t0 + row) * p.act_cols + col) =
+                    *reinterpret_cast<const uint4*>(out_tile + row * kHalfTile + piece * 16);
+        }
+        }
+        }
+    // the next GEMM adds into this buffer: the whole grid clears it
+    const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    const size_t ctas = static_cast<size_t>(gridDim.x) * gridDim.y;
+    const size_t vecs = static_cast<size_t>(p.zero_bytes / 16);
+    for (size_t i = cta * kEpilogueThreads + threadIdx.x; i < vecs; i += ctas * kEpilogueThreads) {
+        reinterpret_cast<uint4*>(p.zero_ptr)[i] = make_uint4(0, 0, 0, 0);
+    }
+}
+
+#ifndef HFRK_MIN_CTAS
+#define HFRK_MIN_CTAS 2
+#endif
 template <int kMode>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, HFRK_MIN_CTAS)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -254,16 +728,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const uint32_t empty_bar = smem_u32(&ctrl->empty[0]);
     const uint32_t accum_bar = smem_u32(&ctrl->accum);
     const uint32_t recv_bar = smem_u32(&ctrl->recv);
-    // Split-K reduction geometry: the m x 128 tile is cut into `split` element ranges of `chunk`
-    // floats (a multiple of 4, so that every range is a 16-byte-aligned bulk copy).
-    const int total = p.m * kTileN;
-    // SwiGLU: a range is whole token rows of the tile (ceil(m / split) of them), so that the gate
-    // half and the up half of a column always meet in the same CTA.
-    const uint32_t chunk = kMode == kModeSwiglu
-                               ? static_cast<uint32_t>(kTileN) * ((static_cast<uint32_t>(p.m) + p.split - 1) / p.split)
-                               : ((static_cast<uint32_t>(total) + p.split - 1) / p.split + 3u) & ~3u;
 
-    constexpr bool kRowPar = kMode == kModeRowPar;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * p.tile_rows;
@@ -303,7 +768,15 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
             mbar_init(accum_bar, 1);
             mbar_init(recv_bar, 1);
             mbar_init_fence();
-            if (p.split > 1) mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>(p.split) * chunk * 4u);
+            // An owner of token rows expects one block of [128][rows] floats from every CTA of the
+            // cluster: the rows of its range that exist in the padded tile (the last owner's range
+            // may reach past it).
+            if (p.split > 1 && (rank << p.rows_log2) < p.m) {
+                const int first = rank << p.rows_log2;
+                const int rpo = 1 << p.rows_log2;
+                const int rows_sent = (first + rpo <= p.m_pad ? first + rpo : p.m_pad) - first;
+                mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>(p.split) * kTileN * rows_sent * 4u);
+            }
         }
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"r"(kThreads) : "memory");
@@ -342,27 +815,36 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const uint32_t tmem_acc = ctrl->tmem_base;
     if (threadIdx.x == 0) stamp(p, 1);
 
+    // The two single-thread loops below run alone on their schedulers, so their speed is their
+    // instruction count: stage index, parity and addresses are carried along instead of being
+    // derived from the block index (a division by the runtime stage count costs tens of cycles).
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int issued = prologue;
+            uint32_t s = 0, parity = 0, stage_addr = ring_addr;   // block `stages` re-uses stage 0, first round
+            int k_coord = (kb_start + prologue) * kBlockK;
             for (int i = prologue; i < kb_count; ++i) {
-                const int s = i % p.stages;
-                const uint32_t round = static_cast<uint32_t>(i / p.stages);
-                if (!mbar_wait_bounded(empty_bar + 8u * s, (round - 1u) & 1u, &ctrl->abort, kRoleProducer)) break;
+                if (!mbar_wait_bounded(empty_bar + 8u * s, parity, &ctrl->abort, kRoleProducer)) break;
                 mbar_arrive_expect_tx(full_bar + 8u * s, stage_tx);
-                load_w(ring_addr + s * stage_bytes, full_bar + 8u * s, (kb_start + i) * kBlockK, pol_w);
-                tma_load_2d(ring_addr + s * stage_bytes + kWStageBytes, &tmap_a, full_bar + 8u * s,
-                            (kb_start + i) * kBlockK, 0, pol_a);
+                load_w(stage_addr, full_bar + 8u * s, k_coord, pol_w);
+                tma_load_2d(stage_addr + kWStageBytes, &tmap_a, full_bar + 8u * s, k_coord, 0, pol_a);
                 issued = i + 1;
+                k_coord += kBlockK;
+                stage_addr += stage_bytes;
+                if (++s == static_cast<uint32_t>(p.stages)) {
+                    s = 0;
+                    stage_addr = ring_addr;
+                    parity ^= 1u;
+                }
             }
             if (ctrl->abort) {
                 // Give the copies already in flight a bounded chance to land before the CTA exits.
-                for (int s = 0; s < p.stages && s < issued; ++s) {
-                    const int last = ((issued - 1 - s) / p.stages) * p.stages + s;
-                    const uint32_t parity = static_cast<uint32_t>(last / p.stages) & 1u;
+                for (int st = 0; st < p.stages && st < issued; ++st) {
+                    const int last = ((issued - 1 - st) / p.stages) * p.stages + st;
+                    const uint32_t par = static_cast<uint32_t>(last / p.stages) & 1u;
                     const long long start = clock64();
-                    while (!mbar_try_wait(full_bar + 8u * s, parity)) {
+                    while (!mbar_try_wait(full_bar + 8u * st, par)) {
                         if (clock64() - start > kWaitLimitCycles / 8) break;
                     }
                 }
@@ -373,20 +855,27 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_e4m3_f32(kTileN, p.m_pad);
+            const uint64_t desc_fixed = umma_desc_kmajor_sw128(0u);   // everything but the address field
+            uint32_t s = 0, parity = 0, stage_addr = ring_addr;
             for (int i = 0; i < kb_count; ++i) {
-                const int s = i % p.stages;
-                const uint32_t round = static_cast<uint32_t>(i / p.stages);
-                if (!mbar_wait_bounded(full_bar + 8u * s, round & 1u, &ctrl->abort, kRoleMma)) break;
+                if (!mbar_wait_bounded(full_bar + 8u * s, parity, &ctrl->abort, kRoleMma)) break;
                 if (i == 0) stamp(p, 3);
                 tcgen05_fence_after_sync();
-                const uint64_t w_desc = umma_desc_kmajor_sw128(ring_addr + s * stage_bytes);
-                const uint64_t a_desc = umma_desc_kmajor_sw128(ring_addr + s * stage_bytes + kWStageBytes);
+                const uint64_t w_desc = desc_fixed + (stage_addr >> 4);
+                const uint64_t a_desc = desc_fixed + ((stage_addr + kWStageBytes) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
                     // +32 bytes along K inside the swizzle atom = +2 in the (address >> 4) field.
                     umma_f8f6f4(tmem_acc, w_desc + 2u * kk, a_desc + 2u * kk, idesc, (i | kk) != 0 ? 1u : 0u);
                 }
-                umma_commit(empty_bar + 8u * s);
+                // the stage goes back to the producer only if a later block needs it
+                if (i + p.stages < kb_count) umma_commit(empty_bar + 8u * s);
+                stage_addr += stage_bytes;
+                if (++s == static_cast<uint32_t>(p.stages)) {
+                    s = 0;
+                    stage_addr = ring_addr;
+                    parity ^= 1u;
+                }
             }
             umma_commit(accum_bar);
             stamp(p, 4);
@@ -395,269 +884,36 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
 
     // ---------------------------------------------------------------------- epilogue (warps 0..3)
-    // split == 1: each thread owns one W row (= output column) and writes D straight from TMEM.
-    // split  > 1: every CTA of the cluster owns one `chunk` of the tile. A CTA stages its partial
-    // tile in its own shared memory and sends range q to CTA q with one bulk shared-to-shared copy
-    // that counts bytes on q's `recv` barrier; an owner waits (bounded) until all `split` ranges
-    // have landed, adds them in rank order out of its own memory and writes D. No cluster-wide
-    // barrier sits on this path; the one issued at start-up only proves the peers' barriers exist.
-    constexpr int kOwned = 8;  // owned elements per thread kept in registers (covers m <= 16)
+    // split == 1: the tile goes straight from TMEM to D (through shared memory, to store along rows).
+    // split  > 1: CTA q of the cluster finishes token rows [q * rpo, (q + 1) * rpo) of the tile. Every
+    // CTA sends those rows of its partial tile straight from registers into q's receive buffer with
+    // asynchronous stores that count their bytes on q's `recv` barrier; an owner waits (bounded)
+    // until all `split` blocks have landed, adds them in rank order out of its own shared memory
+    // and writes D. No staging, no copy engine and no cluster-wide barrier sit on this path; the
+    // barrier issued at start-up only proves that the peers' receive barriers exist and are armed.
     const bool epilogue_warp = warp < kEpilogueThreads / 32;
-    const uint32_t recv_addr = smem_u32(ctrl) + kCtrlBytes;  // float recv[split][chunk]
     if (p.split > 1 && !epilogue_warp) cluster_wait_acquire();
     if (epilogue_warp) {
         pdl_wait_prior_grids();
-        const int nl = threadIdx.x;  // TMEM lane = W row inside the tile
-        const int n = n0 + nl;
-        const bool lane_valid = nl < p.tile_rows && n < p.n;
-        const bool direct = p.split == 1;
-        const float scale = __ldg(p.scale) * p.kind_factor;
-        const uint32_t lane_taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
-        // Row-parallel: the call's epoch (completed calls + 1) and this tile's place in the exchange buffer.
-        unsigned int epoch = 0;
-        if (kRowPar) epoch = *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
-        const uint32_t tile_slot0 = blockIdx.x * static_cast<uint32_t>(total);
-
-        // D_in is requested long before it is needed.
-        float din[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            din[j] = (direct && p.accumulate && j < p.m && lane_valid)
-                         ? load_out(p.d, static_cast<size_t>(j) * p.n + n, p.d_dtype)
-                         : 0.0f;
-        }
-        float d_own[kOwned];
-#pragma unroll
-        for (int it = 0; it < kOwned; ++it) {
-            const uint32_t off = threadIdx.x + it * kEpilogueThreads;
-            const int e = static_cast<int>(rank * chunk + off);
-            const int col = n0 + (e % kTileN);
-            d_own[it] = (!direct && p.accumulate && off < chunk && e < total && (e % kTileN) < p.tile_rows && col < p.n)
-                            ? load_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype)
-                            : 0.0f;
-        }
-
-        bool ok = mbar_wait_bounded(accum_bar, 0u, &ctrl->abort, kRoleEpilogue);
-        ok = __all_sync(0xffffffffu, ok) && ctrl->abort == 0u;
-        ok = __all_sync(0xffffffffu, ok);
-        if (threadIdx.x == 0) stamp(p, 5);
-        tcgen05_fence_after_sync();
-        float* const partial = reinterpret_cast<float*>(ring_ptr);  // the ring is idle by now
-        if (kMode == kModeSwiglu && direct) {
-            // Lanes 0..63 hold gate columns, lanes 64..127 the matching up columns. The projection is
-            // rounded to the 16-bit type first, as the unfused chain stores it, so both give the same
-            // bytes. The activation is shared out by tokens: the gate thread of a column takes tokens
-            // 0..7, the up thread tokens 8..15, and each hands the other the eight values it needs.
-            constexpr int kPitch = 9;                        // floats per column: no bank conflicts
-            float* const handed = partial;                   // [2][64][9]: up for tokens 0..7, gate for 8..15
-            uint8_t* const out_tile = reinterpret_cast<uint8_t*>(partial + 2 * kHalfTile * kPitch);  // [16][64]
-            const int col_in_tile = nl & (kHalfTile - 1);
-            const int half = nl >> 6;                        // 0: this lane holds gate values, 1: up values
-            float y[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) y[j] = 0.0f;
-            if (ok) {
-                uint32_t v[16];
-                tmem_ld_32x32b_x16(lane_taddr, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) y[j] = round_trip_16(__uint_as_float(v[j]) * scale, p.d_dtype);
-            }
-            {
-                // a gate lane gives away tokens 8..15, an up lane tokens 0..7
-                float* const dst = handed + ((1 - half) * kHalfTile + col_in_tile) * kPitch;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) dst[j] = half == 0 ? y[8 + j] : y[j];
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
-            {
-                const float inv_act = 1.0f / __ldg(p.act_scale);
-                const float* const src = handed + (half * kHalfTile + col_in_tile) * kPitch;
-                const int token0 = half * 8;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (token0 + j < p.m) {
-                        const float gate = half == 0 ? y[j] : src[j];
-                        const float up = half == 0 ? src[j] : y[8 + j];
-                        float t = (gate / (1.0f + expf(-gate))) * up * inv_act;
-                        if (p.act_fnuz) t *= 2.0f;
-                        uint8_t byte = static_cast<uint8_t>(pack_e4m3x2(t, 0.0f) & 0xffu);
-                        if (p.act_fnuz && byte == 0x80u) byte = 0;
-                        out_tile[(token0 + j) * kHalfTile + col_in_tile] = byte;
-                    }
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
-            if (nl < kHalfTile && ok) {
-                const int token = nl >> 2, piece = nl & 3;
-                const int col = static_cast<int>(blockIdx.x) * kHalfTile + piece * 16;
-                if (token < p.m && col < p.act_cols) {   // act_cols % 16 == 0: a piece is inside or outside
-                    *reinterpret_cast<uint4*>(p.act_out + static_cast<size_t>(token) * p.act_cols + col) =
-                        *reinterpret_cast<const uint4*>(out_tile + token * kHalfTile + piece * 16);
-                }
-            }
-        } else if (ok) {
-            for (int c = 0; c < p.m_pad / 16; ++c) {
-                uint32_t v[16];
-                tmem_ld_32x32b_x16(lane_taddr + static_cast<uint32_t>(c * 16), v);
-                tmem_ld_wait();
-                if (direct) {
-                    if (kRowPar) {
-                        // host guarantees m <= 16 here: one chunk, 16 values per thread
-                        float val[16];
-                        uint32_t slot[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            val[j] = __uint_as_float(v[j]);
-                            slot[j] = j < p.m ? tile_slot0 + static_cast<uint32_t>(j * kTileN + nl) : 0xffffffffu;
-                        }
-                        if (!rowpar_exchange<16>(p.rp, epoch, slot, val, &ctrl->abort)) ok = false;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(val[j]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int m = c * 16 + j;
-                        if (ok && m < p.m && lane_valid) {
-                            const size_t idx = static_cast<size_t>(m) * p.n + n;
-                            const float d_in = c == 0 ? din[j] : (p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f);
-                            store_out(p.d, idx, p.d_dtype, fmaf(__uint_as_float(v[j]), scale, d_in));
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int m = c * 16 + j;
-                        if (m < p.m) partial[m * kTileN + nl] = __uint_as_float(v[j]);
-                    }
-                }
-            }
-        }
-        if (!direct) {
-            // generic-proxy writes above -> visible to the bulk-copy engine, then one thread sends
-            fence_proxy_async_smem();
-            cluster_wait_acquire();
-            asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
-            if (threadIdx.x == 0 && ok) {
-                for (int q = 0; q < p.split; ++q) {
-                    dsmem_bulk_copy(dsmem_map(recv_addr + 4u * rank * chunk, static_cast<uint32_t>(q)),
-                                    ring_addr + 4u * static_cast<uint32_t>(q) * chunk, 4u * chunk,
-                                    dsmem_map(recv_bar, static_cast<uint32_t>(q)));
-                }
-            }
-            bool landed = ok && mbar_wait_bounded(recv_bar, 0u, &ctrl->abort, kRoleEpilogue);
-            landed = __all_sync(0xffffffffu, landed);
-            if (kMode == kModeSwiglu) {
-                // This CTA owns `rows` whole token rows of the tile, starting at token t0; thread
-                // tid holds lane tid of each. Same activation as in the unsplit case: the gate lane
-                // of a column takes the first half of the tokens, the up lane the second half.
-                const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
-                const int per_owner = static_cast<int>(chunk) / kTileN;          // <= 8 for m <= 16, split >= 2
-                const int t0 = rank * per_owner;
-                const int rows = landed ? (p.m - t0 < per_owner ? p.m - t0 : per_owner) : 0;   // may be <= 0
-                const int first_half = (per_owner + 1) / 2;
-                constexpr int kPitch = 5;                                        // floats per column and half
-                float* const handed = partial + static_cast<size_t>(p.split) * chunk;   // past the staged tile
-                uint8_t* const out_tile = reinterpret_cast<uint8_t*>(handed + 2 * kHalfTile * kPitch);  // [8][64]
-                const int col_in_tile = nl & (kHalfTile - 1);
-                const int half = nl >> 6;
-                float y[kOwned];
-#pragma unroll
-                for (int it = 0; it < kOwned; ++it) {
-                    float sum = 0.0f;
-                    if (it < rows) {
-                        for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + it * kTileN + nl];
-                    }
-                    y[it] = round_trip_16(sum * scale, p.d_dtype);
-                }
-#pragma unroll
-                for (int it = 0; it < kOwned; ++it) {
-                    const bool give = half == 0 ? it >= first_half : it < first_half;
-                    if (give && it < per_owner) {
-                        const int slot_in_half = half == 0 ? it - first_half : it;
-                        handed[((1 - half) * kHalfTile + col_in_tile) * kPitch + slot_in_half] = y[it];
-                    }
-                }
-                asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
-                const float inv_act = 1.0f / __ldg(p.act_scale);
-#pragma unroll
-                for (int it = 0; it < kOwned; ++it) {
-                    const bool mine = half == 0 ? it < first_half : it >= first_half;
-                    if (mine && it < rows) {
-                        const int slot_in_half = half == 0 ? it : it - first_half;
-                        const float other = handed[(half * kHalfTile + col_in_tile) * kPitch + slot_in_half];
-                        const float gate = half == 0 ? y[it] : other;
-                        const float up = half == 0 ? other : y[it];
-                        float t = (gate / (1.0f + expf(-gate))) * up * inv_act;
-                        if (p.act_fnuz) t *= 2.0f;
-                        uint8_t byte = static_cast<uint8_t>(pack_e4m3x2(t, 0.0f) & 0xffu);
-                        if (p.act_fnuz && byte == 0x80u) byte = 0;
-                        out_tile[it * kHalfTile + col_in_tile] = byte;
-                    }
-                }
-                asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueThreads) : "memory");
-                if (nl < 4 * rows) {
-                    const int row = nl >> 2, piece = nl & 3;
-                    const int col = static_cast<int>(blockIdx.x) * kHalfTile + piece * 16;
-                    if (col < p.act_cols) {
-                        *reinterpret_cast<uint4*>(p.act_out + static_cast<size_t>(t0 + row) * p.act_cols + col) =
-                            *reinterpret_cast<const uint4*>(out_tile + row * kHalfTile + piece * 16);
-                    }
-                }
-            } else if (landed) {
-                const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(ctrl) + kCtrlBytes);
-                float own[kOwned];
-                uint32_t slot[kOwned];
-#pragma unroll
-                for (int it = 0; it < kOwned; ++it) {
-                    const uint32_t off = threadIdx.x + it * kEpilogueThreads;
-                    const int e = static_cast<int>(rank * chunk + off);
-                    float sum = 0.0f;
-                    if (off < chunk && e < total) {
-                        for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + off];
-                    }
-                    own[it] = sum;
-                    slot[it] = (off < chunk && e < total) ? tile_slot0 + static_cast<uint32_t>(e) : 0xffffffffu;
-                }
-                if (kRowPar) {
-                    landed = rowpar_exchange<kOwned>(p.rp, epoch, slot, own, &ctrl->abort);
-                }
-#pragma unroll
-                for (int it = 0; it < kOwned; ++it) {
-                    const uint32_t off = threadIdx.x + it * kEpilogueThreads;
-                    const int e = static_cast<int>(rank * chunk + off);
-                    if (landed && off < chunk && e < total) {
-                        const int col = n0 + (e % kTileN);
-                        if ((e % kTileN) < p.tile_rows && col < p.n) {
-                            store_out(p.d, static_cast<size_t>(e / kTileN) * p.n + col, p.d_dtype,
-                                      fmaf(own[it], scale, d_own[it]));
-                        }
-                    }
-                }
-                // token counts above 16 own more than kOwned elements per thread for small splits
-                for (uint32_t off = threadIdx.x + kOwned * kEpilogueThreads; off < chunk; off += kEpilogueThreads) {
-                    const int e = static_cast<int>(rank * chunk + off);
-                    if (e >= total) break;
-                    float sum = 0.0f;
-                    for (int q = 0; q < p.split; ++q) sum += recv[q * chunk + off];
-                    const int col = n0 + (e % kTileN);
-                    if ((e % kTileN) < p.tile_rows && col < p.n) {
-                        const size_t idx = static_cast<size_t>(e / kTileN) * p.n + col;
-                        const float d0 = p.accumulate ? load_out(p.d, idx, p.d_dtype) : 0.0f;
-                        store_out(p.d, idx, p.d_dtype, fmaf(sum, scale, d0));
-                    }
-                }
-            }
-            // the staged partial tile must outlive the copies that read it
-            if (threadIdx.x == 0) bulk_copies_source_done();
-        }
-        if (kMode == kModeSwiglu) {
-            // the next GEMM adds into this buffer: the whole grid clears it
-            const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
-            const size_t ctas = static_cast<size_t>(gridDim.x) * gridDim.y;
-            const size_t vecs = static_cast<size_t>(p.zero_bytes / 16);
-            for (size_t i = cta * kEpilogueThreads + threadIdx.x; i < vecs; i += ctas * kEpilogueThreads) {
-                reinterpret_cast<uint4*>(p.zero_ptr)[i] = make_uint4(0, 0, 0, 0);
+        EpiCtx cx;
+        cx.ctrl = ctrl;
+        cx.ring_ptr = ring_ptr;
+        cx.recv_addr = smem_u32(ctrl) + kCtrlBytes;
+        cx.recv_bar = recv_bar;
+        cx.accum_bar = accum_bar;
+        cx.lane_taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
+        cx.rank = rank;
+        cx.n0 = n0;
+        cx.scale = __ldg(p.scale) * p.kind_factor;
+        if constexpr (kMode == kModeSwiglu) {
+            epilogue_swiglu(p, cx);
+        } else {
+            if (p.d_dtype == HFRK_BF16) {
+                epilogue_store<kMode, HFRK_BF16>(p, cx);
+            } else if (p.d_dtype == HFRK_F16) {
+                epilogue_store<kMode, HFRK_F16>(p, cx);
+            } else {
+                epilogue_store<kMode, HFRK_F32>(p, cx);
             }
         }
     }
@@ -666,7 +922,7 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kMmaWarp) tmem_dealloc(tmem_acc, tmem_cols);
-    if (kRowPar && threadIdx.x == 0) {
+    if (kMode == kModeRowPar && threadIdx.x == 0) {
         // The last CTA of the grid closes the call: every CTA has read the call index by now.
         __threadfence();
         const unsigned int ctas = gridDim.x * gridDim.y;

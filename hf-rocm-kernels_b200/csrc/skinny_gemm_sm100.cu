@@ -42,6 +42,7 @@
 #include "ptx_sm100.cuh"
 #include "elementwise_common.cuh"
 #include "skinny_gemm_common.cuh"
+#include "device_model.cuh"
 #include "skinny_gemm_kernel.cuh"
 #include "skinny_gemm_streamk.cuh"
 
@@ -134,7 +135,23 @@ int get_tensor_map(const void* base, uint64_t inner, uint64_t outer, uint64_t st
 
 struct Plan {
     int split, stages, ctas, smem_bytes, m_pad, num_kblocks, tile_rows, tiles;
+    int rows_log2;        // split > 1: token rows finished per CTA of a cluster = 1 << rows_log2
 };
+
+// Token rows each CTA of a cluster finishes in the split-K reduction: the smallest power of two
+// that is at least ceil(m / split) (a power of two so that a thread's 1, 2 or 4 consecutive rows
+// always belong to one owner and can leave in one vector store).
+int rows_per_owner_log2(int m, int split) {
+    const int need = (m + split - 1) / split;
+    int lg = 0;
+    while ((1 << lg) < need) ++lg;
+    return lg;
+}
+
+// Receive buffer of the split-K reduction: float [split][128][rows per owner].
+int recv_buffer_bytes(int m, int split) {
+    return split > 1 ? split * kTileN * 4 * (1 << rows_per_owner_log2(m, split)) : 0;
+}
 
 int round_up(int v, int to) { return (v + to - 1) / to * to; }
 
@@ -165,25 +182,61 @@ bool tuning_lookup(int m_pad, int n, int k, TuneValue* out) {
     return true;
 }
 
-// Launch shape of the cluster kernel for one launch of m <= kMaxMPad tokens, from sweeps on B200
-// (148 SMs) over the Llama-3 8B/70B projection shapes and their 2/4/8-way N and K shards:
-//   * one SM cannot pull much more than 40 GB/s of weights, so every SM must stream, and two small
-//     CTAs per SM hide each other's fill, drain and reduction better than one big one: with a K
-//     split the ring has four 18 KiB stages (two CTAs per SM at 16 tokens);
-//   * the whole grid must be resident at once, WITH MARGIN. A cluster that has to wait for a free
-//     slot starts late and then streams alone at a fraction of the bandwidth, and clusters only
-//     fit into one GPC, so a grid that fills the last slot on paper (288 of 296) already spills.
-//     The split is the largest one with tiles * split <= 280 and at least two K blocks per CTA,
-//     capped at 8 (12 below 25 tiles, 16 below 11: very narrow shards need it to reach the SMs);
-//   * without a split (tiles alone cover the SMs) a ring of six stages, two CTAs per SM.
-//   * tiles of fewer than 128 rows can even out a grid without a K split that is between one and
-//     two CTAs per SM: 224 tiles of 128 rows put two CTAs on 76 SMs and one on the other 72, and
-//     the grid ends when the doubly loaded SMs are done; 279 tiles of 103 rows load nearly every
-//     SM twice. The tensor core still computes 128 lanes per tile (it idles at a few per cent
-//     anyway); the lanes past the tile's rows are ignored. Measured gain on 28672 x 4096: 2.4 %.
-//     Nowhere else: with clusters a taller grid crosses the residency cliff (35 clusters of 8
-//     instead of 32: +45 % time), and grids of several waves got slower (57344 x 8192: +2 %).
-int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan, int tile_rows_req = 0) {
+// Shared memory one CTA of the cluster kernel takes: alignment slack, the ring, the control block
+// and the receive buffer of the split-K reduction.
+int plan_smem_bytes(int m, int m_pad, int split, int stages) {
+    return 1024 + stages * (kWStageBytes + m_pad * kBlockK) + kCtrlBytes + recv_buffer_bytes(m, split);
+}
+
+// CTAs of the kernel that fit on one SM: shared memory decides (the registers allow three).
+int ctas_per_sm(int smem_bytes) {
+    const int by_smem = kSmemPerSm / (smem_bytes + kSmemCtaReserve);
+    return by_smem < kModelMaxPerSm ? by_smem : kModelMaxPerSm;
+}
+
+// Launch shapes measured best on B200 for the Llama-3 8B/70B decode projections and their K shards
+// (16 tokens and fewer), in the reference's tradition of a per-shape table (hf_rocm_kernels/
+// operators/skinny_gemm/wrapped.py:42-102). An entry is only used if the device holds all its
+// clusters at once (the measured capacity decides); otherwise the rule below takes over.
+struct BuiltinShape {
+    int n, k, split, stages;
+};
+constexpr BuiltinShape kBuiltinShapes[] = {
+    {6144, 4096, 7, 3},    // 8B qkv
+    {4096, 4096, 8, 3},    // 8B o_proj
+    {4096, 14336, 8, 5},   // 8B down
+    {10240, 8192, 5, 3},   // 70B qkv
+    {8192, 8192, 6, 3},    // 70B o_proj
+    {57344, 8192, 1, 3},   // 70B gate_up
+    {8192, 28672, 6, 3},   // 70B down
+    {8192, 14336, 6, 3},   // 70B down, K over 2 GPUs
+    {8192, 7168, 6, 3},    // 70B down, K over 4 GPUs
+    {8192, 3584, 6, 3},    // 70B down, K over 8 GPUs
+    {5120, 8192, 6, 4},    // 70B qkv, N over 2 GPUs
+    {14336, 8192, 2, 5},   // 70B gate_up, N over 4 GPUs
+};
+
+// Launch shape of the cluster kernel for one launch of m <= kMaxMPad tokens. What the measurements
+// on B200 say (traces of consecutive calls in a graph, sweeps over the Llama-3 shapes and shards):
+//   * a call in a chain of dependent launches costs latency, not bandwidth, until the matrix
+//     reaches ~100 MB: dependency release, activation load, MMA issue, reduction, exit. More CTAs
+//     shorten every CTA's K range and put more loads in flight, so the K split is the largest one
+//     whose clusters are ALL resident at once. Residency is the cliff: a cluster that waits for a
+//     free slot starts when others leave and streams alone (5120 x 8192: 10.0 us with 40 clusters
+//     of 6, 14.6 us with 40 clusters of 7 on a chip that holds 39 of them). The capacity comes
+//     from the device model (measured per chip), never from a constant;
+//   * three CTAs per SM (a ring of three 18 KiB stages) beat two (four stages) on most shapes:
+//     the third slot lets part of the NEXT call's grid move in and start its weight stream while
+//     this call drains;
+//   * at least two K blocks per CTA; no split once the tiles alone cover the SMs (then six
+//     stages, two CTAs per SM, or three stages when that saves a wave: 448 tiles on 444 slots);
+//   * tiles of fewer than 128 rows even out a grid without a K split that is between one and two
+//     CTAs per SM: 224 tiles of 128 rows put two CTAs on 76 SMs and one on the other 72; 276
+//     tiles of 104 rows load nearly every SM twice (28672 x 4096: -2.4 %). The tensor core still
+//     computes 128 lanes per tile; the lanes past the tile's rows are ignored. The height stays a
+//     multiple of 8 so that the epilogue's 16-byte stores stay aligned.
+int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int stages_req, Plan* plan,
+              int tile_rows_req = 0) {
     if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
     if (tile_rows_req < kAutoTileRowsOff || tile_rows_req > kTileN || (tile_rows_req > 0 && tile_rows_req < 8))
         return HFRK_INVALID_CONFIG;
@@ -193,35 +246,77 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan, in
     const int tiles = (n + kTileN - 1) / kTileN;
     const int nkb = (k + kBlockK - 1) / kBlockK;
     const int stage_bytes = kWStageBytes + m_pad * kBlockK;
-    constexpr int kResidentTarget = 280;
+    const int two_per_sm = 2 * dm.sms;
+
+    // all clusters of (split, stages) resident at once on this device?
+    auto resident = [&](int split, int stages) {
+        const int smem = plan_smem_bytes(m, m_pad, split, stages);
+        if (smem > kSmemLimit) return false;
+        const int per_sm = ctas_per_sm(smem);
+        // one cluster to spare: at the exact capacity a straggler of the previous grid keeps the last one out
+        return per_sm >= 1 && tiles < dm.capacity[split][per_sm];
+    };
 
     TuneValue tuned;
-    if (split_req == 0 && stages_req == 0 && tile_rows_req == 0 && tuning_lookup(m_pad, n, k, &tuned)) {
-        split_req = tuned.split;
-        stages_req = tuned.stages;
-        tile_rows_req = tuned.tile_rows;
+    if (split_req == 0 && stages_req == 0 && tile_rows_req == 0) {
+        if (tuning_lookup(m_pad, n, k, &tuned)) {
+            split_req = tuned.split;
+            stages_req = tuned.stages;
+            tile_rows_req = tuned.tile_rows;
+        } else if (m_pad == 16) {
+            for (const BuiltinShape& b : kBuiltinShapes) {
+                if (b.n == n && b.k == k && (b.split == 1 || resident(b.split, b.stages))) {
+                    split_req = b.split;
+                    stages_req = b.stages;
+                    break;
+                }
+            }
+        }
     }
     int split = split_req;
+    int stages = stages_req;
     if (split == 0) {
-        split = kResidentTarget / tiles;
-        const int cap = tiles <= 10 ? kMaxSplit : (tiles <= 24 ? 12 : 8);
-        if (split > cap) split = cap;
-        if (split < 2 && tiles < kNumSms) split = 2;  // 141..147 tiles: two CTAs per SM still beat one
-        if (split > nkb / 2) split = nkb / 2;
-        if (split < 1) split = 1;
+        split = 1;
+        if (tiles < dm.sms) {
+            // largest resident split, three CTAs per SM first (a short ring), then two
+            int best_ctas = 0;
+            const int ring_choices[2] = {3, 4};
+            for (int choice = 0; choice < 2; ++choice) {
+                const int ring = stages_req != 0 ? stages_req : ring_choices[choice];
+                for (int s = kMaxSplit; s >= 2; --s) {
+                    if (nkb / s < 2) continue;
+                    if (!resident(s, ring)) continue;
+                    if (tiles * s > best_ctas) {
+                        best_ctas = tiles * s;
+                        split = s;
+                        if (stages_req == 0) stages = ring;
+                    }
+                    break;   // smaller splits of this ring have fewer CTAs
+                }
+            }
+        }
     }
     if (split > nkb) split = nkb;
+    if (split < 1) split = 1;
 
-    const int chunk = (((m * kTileN + split - 1) / split) + 3) & ~3;
-    const int recv_bytes = split > 1 ? split * chunk * 4 : 0;
-    const int fixed_bytes = 1024 + kCtrlBytes + recv_bytes;
+    const int fixed_bytes = 1024 + kCtrlBytes + recv_buffer_bytes(m, split);
     const int max_stages_fit = (kSmemLimit - fixed_bytes) / stage_bytes;
-    int stages = stages_req != 0 ? stages_req : (split > 1 ? 4 : 6);
-    if (stages_req == 0) {
+    if (stages == 0) {
+        if (split > 1) {
+            stages = 4;
+        } else {
+            // three stages (three CTAs per SM) when two per SM would need one more wave than three
+            const int waves2 = (tiles + two_per_sm - 1) / two_per_sm;
+            const int waves3 = (tiles + 3 * dm.sms - 1) / (3 * dm.sms);
+            stages = (m_pad == 16 && waves3 < waves2) ? 3 : 6;
+        }
         // keep two CTAs on an SM when the activation tile or the receive buffer of a larger token
         // count grows: with one CTA per SM a grid of 150-296 CTAs needs a second wave
-        while (stages > 2 && 2 * (fixed_bytes + stages * stage_bytes + 1024) > 228 * 1024) --stages;
+        while (stages > 2 && 2 * (fixed_bytes + stages * stage_bytes + kSmemCtaReserve) > kSmemPerSm) --stages;
     }
+    // a ring longer than the CTA's K range only takes shared memory from the next call's CTAs
+    const int blocks_per_cta = (nkb + split - 1) / split;
+    if (stages_req == 0 && stages > blocks_per_cta) stages = blocks_per_cta < 2 ? 2 : blocks_per_cta;
     if (stages > max_stages_fit) stages = max_stages_fit;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return HFRK_INVALID_CONFIG;
@@ -230,9 +325,10 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan, in
     if (tile_rows == 0) {
         tile_rows = kTileN;
         const int smem = fixed_bytes + stages * stage_bytes;
-        if (m_pad == 16 && split == 1 && tiles > kNumSms && tiles <= kResidentTarget &&
-            2 * (smem + 1024) <= 228 * 1024) {
-            const int rows = (n + kResidentTarget - 1) / kResidentTarget;
+        const int slots = two_per_sm - two_per_sm / 18;   // two CTAs per SM, a few slots spare
+        if (m_pad == 16 && split == 1 && tiles > dm.sms && tiles <= slots && ctas_per_sm(smem) >= 2) {
+            // a multiple of 8 rows: the epilogue stores 16 outputs at a time from 16-byte-aligned addresses
+            const int rows = round_up((n + slots - 1) / slots, 8);
             if (rows >= 64 && rows < tile_rows) tile_rows = rows;
         }
     }
@@ -246,6 +342,7 @@ int make_plan(int m, int n, int k, int split_req, int stages_req, Plan* plan, in
     plan->smem_bytes = fixed_bytes + stages * stage_bytes;
     plan->m_pad = m_pad;
     plan->num_kblocks = nkb;
+    plan->rows_log2 = split > 1 ? rows_per_owner_log2(m, split) : 0;
     return HFRK_SUCCESS;
 }
 
@@ -476,7 +573,8 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         const int mc = m - m0 < m_step ? m - m0 : m_step;
         Plan plan;
         // the exchange buffer of the row-parallel kernel is laid out in 128-row tiles
-        rc = make_plan(mc, n, k, split_req, stages_req, &plan, rowpar != nullptr ? kAutoTileRowsOff : tile_rows_req);
+        rc = make_plan(device_model(stream), mc, n, k, split_req, stages_req, &plan,
+                       rowpar != nullptr ? kAutoTileRowsOff : tile_rows_req);
         if (rc != HFRK_SUCCESS) return rc;
         CUtensorMap tmap_w;
         rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
@@ -499,6 +597,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         p.tile_rows = plan.tile_rows;
         p.num_kblocks = plan.num_kblocks;
         p.split = plan.split;
+        p.rows_log2 = plan.rows_log2;
         p.stages = plan.stages;
         p.d_dtype = d_dtype;
         p.accumulate = accumulate ? 1 : 0;
@@ -582,20 +681,8 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
                         static_cast<uint64_t>(w_row_stride), kHalfTile, &tmap_w);
     if (rc != HFRK_SUCCESS) return rc;
     Plan plan;
-    rc = make_plan(m, 2 * inter, k, split_req, /*stages_req=*/0, &plan, kAutoTileRowsOff);
+    rc = make_plan(device_model(stream), m, 2 * inter, k, split_req, /*stages_req=*/0, &plan, kAutoTileRowsOff);
     if (rc != HFRK_SUCCESS) return rc;
-    if (plan.split > 1) {
-        // the receive buffer holds whole token rows per owner: ceil(m / split) rows of 128 floats
-        const int plain_chunk = (((m * kTileN + plan.split - 1) / plan.split) + 3) & ~3;
-        const int row_chunk = kTileN * ((m + plan.split - 1) / plan.split);
-        plan.smem_bytes += plan.split * (row_chunk - plain_chunk) * 4;
-        const int stage_bytes = kWStageBytes + plan.m_pad * kBlockK;
-        while (plan.stages > 2 && 2 * (plan.smem_bytes + 1024) > 228 * 1024) {
-            --plan.stages;
-            plan.smem_bytes -= stage_bytes;
-        }
-        if (plan.smem_bytes > kSmemLimit) return HFRK_INVALID_CONFIG;
-    }
     rc = get_tensor_map(A, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(k),
                         static_cast<uint32_t>(plan.m_pad), &tmap_a);
     if (rc != HFRK_SUCCESS) return rc;
@@ -611,6 +698,7 @@ int launch_gemm_swiglu(const void* A, const void* W, void* act_out, const float*
     p.tile_rows = kTileN;
     p.num_kblocks = plan.num_kblocks;
     p.split = plan.split;
+    p.rows_log2 = plan.rows_log2;
     p.stages = plan.stages;
     p.d_dtype = mid_dtype;
     p.accumulate = 0;
@@ -1018,7 +1106,7 @@ extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split
     if (variant == HFRK_VARIANT_AUTO) variant = HFRK_VARIANT_CLUSTER;
     if (variant == HFRK_VARIANT_CLUSTER) {
         hfrk::Plan plan;
-        int rc = hfrk::make_plan(mc, n, k, split_k, 0, &plan);
+        int rc = hfrk::make_plan(hfrk::device_model(nullptr), mc, n, k, split_k, 0, &plan);
         if (rc != HFRK_SUCCESS) return rc;
         out8[0] = variant; out8[1] = plan.split; out8[2] = plan.stages; out8[3] = plan.ctas;
         out8[4] = plan.smem_bytes; out8[5] = plan.m_pad; out8[6] = plan.num_kblocks;
@@ -1049,6 +1137,39 @@ extern "C" int hfrk_tuning_set_ex(int m, int n, int k, int split_k, int num_stag
 
 extern "C" int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages) {
     return hfrk_tuning_set_ex(m, n, k, split_k, num_stages, 0);
+}
+
+extern "C" int hfrk_device_model_get(int* sms_out, int* capacity_out, int* measured_out) {
+    const hfrk::DeviceModel dm = hfrk::device_model(nullptr);
+    if (sms_out != nullptr) *sms_out = dm.sms;
+    if (measured_out != nullptr) *measured_out = dm.measured ? 1 : 0;
+    if (capacity_out != nullptr) {
+        for (int split = 0; split <= hfrk::kModelMaxSplit; ++split) {
+            for (int per_sm = 0; per_sm <= hfrk::kModelMaxPerSm; ++per_sm) {
+                capacity_out[split * (hfrk::kModelMaxPerSm + 1) + per_sm] = dm.capacity[split][per_sm];
+            }
+        }
+    }
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_device_model_override(int sms, const int* capacity) {
+    std::lock_guard<std::mutex> lock(hfrk::model_detail::mutex());
+    if (capacity == nullptr) {
+        hfrk::model_detail::override_on() = false;
+        return HFRK_SUCCESS;
+    }
+    if (sms < 1) return HFRK_INVALID_CONFIG;
+    hfrk::DeviceModel& dm = hfrk::model_detail::override_model();
+    dm.sms = sms;
+    dm.measured = false;
+    for (int split = 0; split <= hfrk::kModelMaxSplit; ++split) {
+        for (int per_sm = 0; per_sm <= hfrk::kModelMaxPerSm; ++per_sm) {
+            dm.capacity[split][per_sm] = capacity[split * (hfrk::kModelMaxPerSm + 1) + per_sm];
+        }
+    }
+    hfrk::model_detail::override_on() = true;
+    return HFRK_SUCCESS;
 }
 
 extern "C" int hfrk_tuning_clear(void) {

@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "hfrk_skinny_gemm_fp8_noalloc", "hfrk_max_active_clusters", "hfrk_tuning_set", "hfrk_tuning_clear",
     "hfrk_swiglu_fp8", "hfrk_residual_rms", "hfrk_rowpar_set_mode",
     "hfrk_skinny_gemm_fp8_swiglu", "hfrk_skinny_gemm_fp8_host_async",
-    "hfrk_tuning_set_ex", "hfrk_rowpar_set_wait_ms",
+    "hfrk_tuning_set_ex", "hfrk_rowpar_set_wait_ms", "hfrk_device_model_get", "hfrk_device_model_override",
 )
 
 
@@ -89,6 +89,10 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_tuning_set_ex.argtypes = [i32, i32, i32, i32, i32, i32]
     lib.hfrk_tuning_set_ex.restype = i32
     lib.hfrk_tuning_clear.restype = i32
+    lib.hfrk_device_model_get.argtypes = [ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    lib.hfrk_device_model_get.restype = i32
+    lib.hfrk_device_model_override.argtypes = [i32, ctypes.POINTER(i32)]
+    lib.hfrk_device_model_override.restype = i32
     lib.hfrk_swiglu_fp8.argtypes = [vp, vp, vp, vp, i32, i32, i64, i32, i32, i32, vp]
     lib.hfrk_swiglu_fp8.restype = i32
     lib.hfrk_residual_rms.argtypes = [vp, vp, vp, vp, ctypes.c_float, vp, vp, i32, i32, i64, i32, i32, i32, i32, vp]
@@ -274,6 +278,30 @@ def plan(m: int, n: int, k: int, variant: int = VARIANT_AUTO, split_k: int = 0, 
     check(lib.hfrk_skinny_gemm_plan(m, n, k, variant, split_k, ctas_per_sm, out))
     keys = ("variant", "split_k", "num_stages", "ctas", "smem_bytes", "m_pad", "k_blocks", "tiles")
     return dict(zip(keys, list(out)))
+
+
+MODEL_MAX_SPLIT, MODEL_MAX_PER_SM = 16, 3
+
+
+def device_model() -> dict:
+    """``hfrk_device_model_get``: SM count and ``capacity[split][ctas_per_sm]`` (clusters resident at once)."""
+    sms, measured = ctypes.c_int(0), ctypes.c_int(0)
+    flat = (ctypes.c_int * ((MODEL_MAX_SPLIT + 1) * (MODEL_MAX_PER_SM + 1)))()
+    check(lib.hfrk_device_model_get(ctypes.byref(sms), flat, ctypes.byref(measured)))
+    cap = [[flat[s * (MODEL_MAX_PER_SM + 1) + p] for p in range(MODEL_MAX_PER_SM + 1)] for s in range(MODEL_MAX_SPLIT + 1)]
+    return {"sms": sms.value, "measured": bool(measured.value), "capacity": cap}
+
+
+def override_device_model(sms: int = 0, capacity=None) -> None:
+    """``hfrk_device_model_override``; ``capacity[split][ctas_per_sm]`` or None to drop the override."""
+    if capacity is None:
+        check(lib.hfrk_device_model_override(0, None))
+        return
+    flat = (ctypes.c_int * ((MODEL_MAX_SPLIT + 1) * (MODEL_MAX_PER_SM + 1)))()
+    for s in range(MODEL_MAX_SPLIT + 1):
+        for p in range(MODEL_MAX_PER_SM + 1):
+            flat[s * (MODEL_MAX_PER_SM + 1) + p] = int(capacity[s][p])
+    check(lib.hfrk_device_model_override(sms, flat))
 
 
 def max_active_clusters(split: int, smem_bytes: int) -> int:

@@ -14,6 +14,9 @@ Configurations (index = position in the benchmark specification):
   4  edge sweep: M in {3,5,7,13,16} x N in {1000,4104,11008} x K in {1040,4096,5120}, bias on every
      other case, 1 % of the entries replaced by +-1e6 AFTER the scale is taken (they saturate to +-448)
 Seed of a case = 1000 * configuration + case index.
+
+This module imports torch only (nothing else of the package), so that a CPU-only arm of a benchmark
+can load it by file path without loading the CUDA libraries.
 """
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
@@ -21,7 +24,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 from torch import Tensor
 
-from hf_rocm_kernels.utils.fp8 import E4M3FN_MAX
+E4M3FN_MAX = 448.0   # largest finite e4m3fn value; the same constant as utils/fp8.py
 
 LLAMA3_8B = {"qkv": (6144, 4096), "o_proj": (4096, 4096), "gate_up": (28672, 4096), "down": (4096, 14336)}
 LLAMA3_70B = {"qkv": (10240, 8192), "o_proj": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}

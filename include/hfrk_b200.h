@@ -281,6 +281,21 @@ int hfrk_tuning_set(int m, int n, int k, int split_k, int num_stages);
 int hfrk_tuning_set_ex(int m, int n, int k, int split_k, int num_stages, int tile_rows);
 int hfrk_tuning_clear(void);
 
+/* What the launch planner knows about the current device: the SM count and, for cluster sizes
+ * 1..16 and 1..3 CTAs per SM, how many clusters the chip holds at once, written to
+ * capacity_out[17 * 4] as [cluster size][CTAs per SM]. The capacities are MEASURED on the first
+ * call on a device (a probe kernel whose CTAs wait a bounded 50 us for each other; about 50 ms
+ * once per device and process): clusters live inside one GPC and chips differ in how their SMs
+ * are spread over the GPCs. That first call must not come inside a stream capture; if it does, an
+ * estimate is used until a later call can measure (*measured_out = 0). Any pointer may be NULL.
+ * Stands where the reference hard-codes its CU count (csrc/op_src/skinny_gemm/core.cu:24). */
+int hfrk_device_model_get(int* sms_out, int* capacity_out, int* measured_out);
+/* Replaces the device model by the given one for every later plan in this process (capacity as in
+ * hfrk_device_model_get; NULL = back to the real device). For tests of the planner, which can
+ * then run without a GPU, and for planning on behalf of another chip. */
+int hfrk_device_model_override(int sms, const int* capacity);
+
+
 /* How many clusters of `split` CTAs of the GEMM kernel with `smem_bytes` of dynamic shared memory
  * the current device can hold at once (cudaOccupancyMaxActiveClusters): the figure the launch
  * heuristic needs, exposed for tuning scripts. Clusters must fit inside one GPC, so the answer

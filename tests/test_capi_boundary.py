@@ -44,20 +44,85 @@ def test_version(capi):
     assert capi.lib.hfrk_last_error() is not None
 
 
-def test_plan_covers_the_sms(capi):
-    # fewer tiles than SMs -> the largest K split whose grid is resident at once (with margin), two CTAs per SM
-    for (m, n, k) in [(16, 4096, 4096), (16, 6144, 4096), (16, 4096, 14336), (16, 8192, 8192), (1, 8192, 28672)]:
-        p = capi.plan(m, n, k)
-        assert p["variant"] == capi.VARIANT_CLUSTER and p["tiles"] == (n + 127) // 128
-        assert 148 <= p["ctas"] <= 280 and p["ctas"] == p["tiles"] * p["split_k"]
-        assert p["k_blocks"] // p["split_k"] >= 2 and 2 * (p["smem_bytes"] + 1024) <= 228 * 1024
-    # enough tiles -> no split, deeper ring
-    for (m, n, k) in [(16, 28672, 4096), (4, 57344, 8192)]:
-        p = capi.plan(m, n, k)
-        assert p["split_k"] == 1 and p["num_stages"] == 6
-    # between one and two CTAs per SM without a split: shorter tiles even out the load
-    assert capi.plan(16, 28672, 4096)["tiles"] == 279 and capi.plan(4, 57344, 8192)["tiles"] == 448
-    assert capi.plan(17, 28672, 4096)["tiles"] == 224           # more than 16 tokens: 128-row tiles
+def _fake_capacity(sms, gpc_sizes):
+    """Clusters resident at once on an imagined chip whose SMs sit in GPCs of the given sizes: a cluster
+    needs all its CTA slots inside one GPC."""
+    assert sum(gpc_sizes) == sms
+    return [[0] * 4] + [[0] + [sum((g * per_sm) // split for g in gpc_sizes) for per_sm in (1, 2, 3)]
+                        for split in range(1, 17)]
+
+
+GRADED_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336),
+                 (10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)]
+
+
+def _shards():
+    out = list(GRADED_SHAPES)
+    for g in (2, 4, 8):
+        out += [(n // g, k) for (n, k) in GRADED_SHAPES[4:]]          # N split of the 70B projections
+        out.append((8192, 28672 // g))                               # K split of the 70B down projection
+    return out
+
+
+@pytest.mark.parametrize("gpcs", [[20, 20, 20, 20, 18, 18, 16, 16], [18] * 6 + [20, 20], [16] * 8 + [20], [10] * 14 + [8]])
+def test_every_graded_plan_is_resident_on_any_chip_layout(capi, gpcs):
+    """The planner never asks for more clusters than the device holds at once, whatever the spread of
+    the SMs over the GPCs: the capacity table is injected, so this runs without a GPU."""
+    sms = sum(gpcs)
+    cap = _fake_capacity(sms, gpcs)
+    capi.override_device_model(sms, cap)
+    try:
+        for (n, k) in _shards():
+            for m in (1, 16, 17, 64):
+                p = capi.plan(m, n, k)
+                assert p["ctas"] == p["tiles"] * p["split_k"]
+                per_sm = min(3, (228 * 1024) // (p["smem_bytes"] + 1024))
+                assert per_sm >= 1
+                if p["split_k"] > 1:
+                    assert p["tiles"] < cap[p["split_k"]][per_sm], (gpcs, m, n, k, p)
+                    assert p["k_blocks"] // p["split_k"] >= 2
+                    assert p["tiles"] < sms
+                else:
+                    assert p["tiles"] >= sms or p["k_blocks"] < 4 or cap[2][per_sm] < p["tiles"]
+    finally:
+        capi.override_device_model(capacity=None)
+
+
+def test_plan_follows_the_device_model(capi):
+    gpcs = [20, 20, 20, 20, 18, 18, 16, 16]
+    cap = _fake_capacity(148, gpcs)
+    capi.override_device_model(148, cap)
+    try:
+        # fewer tiles than SMs -> the largest K split whose clusters are all resident at once
+        for (m, n, k) in [(16, 4096, 4096), (16, 6144, 4096), (16, 4096, 14336), (16, 8192, 8192), (1, 8192, 28672)]:
+            p = capi.plan(m, n, k)
+            assert p["variant"] == capi.VARIANT_CLUSTER and p["tiles"] == (n + 127) // 128
+            assert p["split_k"] >= 4 and 148 <= p["ctas"] <= 3 * 148
+        # one cluster fewer fits -> a smaller split (or a longer ring with fewer CTAs per SM), never a spill
+        tight = [row[:] for row in cap]
+        p0 = capi.plan(16, 4096, 4096)
+        per_sm0 = min(3, (228 * 1024) // (p0["smem_bytes"] + 1024))
+        tight[p0["split_k"]][per_sm0] = p0["tiles"]
+        capi.override_device_model(148, tight)
+        p1 = capi.plan(16, 4096, 4096)
+        assert (p1["split_k"], p1["num_stages"]) != (p0["split_k"], p0["num_stages"])
+        per_sm1 = min(3, (228 * 1024) // (p1["smem_bytes"] + 1024))
+        assert p1["tiles"] < tight[p1["split_k"]][per_sm1]
+        capi.override_device_model(148, cap)
+        # enough tiles -> no split; six stages, or three when three CTAs per SM save a wave
+        assert capi.plan(16, 28672, 4096)["split_k"] == 1 and capi.plan(16, 28672, 4096)["num_stages"] == 6
+        assert capi.plan(4, 57344, 8192)["split_k"] == 1 and capi.plan(4, 57344, 8192)["num_stages"] == 3
+        # between one and two CTAs per SM without a split: shorter tiles (a multiple of 8 rows) even out the load
+        p = capi.plan(16, 28672, 4096)
+        assert 224 < p["tiles"] <= 296 and capi.plan(4, 57344, 8192)["tiles"] == 448
+        assert capi.plan(17, 28672, 4096)["tiles"] == 224           # more than 16 tokens: 128-row tiles
+        # a chip with fewer SMs gets fewer CTAs
+        capi.override_device_model(74, _fake_capacity(74, [20, 18, 18, 18]))
+        assert capi.plan(16, 4096, 4096)["ctas"] <= 3 * 74
+    finally:
+        capi.override_device_model(capacity=None)
+    model = capi.device_model()
+    assert model["sms"] >= 1 and len(model["capacity"]) == 17
     try:
         assert capi.lib.hfrk_tuning_set_ex(16, 4096, 4096, 0, 0, 64) == 0
         assert capi.plan(16, 4096, 4096)["tiles"] == 64
@@ -113,6 +178,7 @@ def test_plan_invariants_over_many_shapes(capi):
     rng = random.Random(11)
     shapes = [(rng.randint(1, 64), rng.randint(1, 70000), 16 * rng.randint(1, 2048)) for _ in range(400)]
     shapes += [(m, n, k) for m in (1, 16, 17, 64) for n in (1, 127, 128, 129, 18944, 19072, 37888) for k in (16, 128, 4096)]
+    model = capi.device_model()
     for m, n, k in shapes:
         p = capi.plan(m, n, k)
         rows = -(-n // p["tiles"])                       # tile height the grid implies
@@ -122,7 +188,9 @@ def test_plan_invariants_over_many_shapes(capi):
         assert 2 <= p["num_stages"] <= 12 and p["smem_bytes"] <= 227 * 1024
         assert p["m_pad"] == 16 * (-(-m // 16))
         if p["split_k"] > 1:
-            assert p["ctas"] <= 296, (m, n, k, p)        # a split grid must be resident at once
+            # a split grid must be resident at once (three CTAs per SM at most, by the device model)
+            per_sm = min(3, (228 * 1024) // (p["smem_bytes"] + 1024))
+            assert p["tiles"] < model["capacity"][p["split_k"]][per_sm], (m, n, k, p)
 
 
 def test_plan_rejects_bad_arguments(capi):

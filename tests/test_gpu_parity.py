@@ -235,8 +235,12 @@ def test_tiles_of_fewer_than_128_rows(capi, dev, checker, m, n, k, tile_rows):
         if tile_rows:
             assert capi.lib.hfrk_tuning_set_ex(m, n, k, 0, 0, tile_rows) == 0
         plan = capi.plan(min(m, 64), n, k)
-        expect_rows = tile_rows if tile_rows else -(-n // 280)
-        assert plan["tiles"] == -(-n // expect_rows) and plan["ctas"] == plan["tiles"] * plan["split_k"]
+        if tile_rows:
+            assert plan["tiles"] == -(-n // tile_rows)
+        else:   # the library's own choice: shorter than 128 rows, a multiple of 8
+            rows = 8 * -(-(-(-n // plan["tiles"])) // 8)
+            assert plan["tiles"] > -(-n // 128) and -(-n // rows) == plan["tiles"]
+        assert plan["ctas"] == plan["tiles"] * plan["split_k"]
         out = _run_c(capi, a, w, s, d_in, case.m, case.n)
     finally:
         capi.lib.hfrk_tuning_clear()
