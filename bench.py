@@ -696,6 +696,11 @@ def multi_gpu_extras(torch, dist, capi, wl, dev, rank, world):
             "us_local_gemm_only": round(local, 2), "nvlink_bytes_out_per_gpu": (world - 1) * 4 * m * n})
     torch.cuda.synchronize()
     dist.barrier()
+    # a timed exchange that ran out of time would leave D untouched and look fast: the status word tells
+    code, word = capi.device_status(clear=True)
+    if not _all_ranks_agree(torch, dist, code == 0, dev):
+        raise RuntimeError(f"a bounded wait ran out during the multi-GPU timing (status word {word:#x} on rank {rank})")
+    out["status_after_timing"] = "ok"
     group.close()
     return out
 

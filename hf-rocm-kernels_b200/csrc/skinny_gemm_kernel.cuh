@@ -31,7 +31,7 @@ static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block grew");
 // Row-parallel (K split over GPUs) exchange state, as seen by the kernel of ONE rank. Every rank
 // owns an exchange buffer that its peers write into over NVLink:
 //   cells : {fp32 value, epoch} [2 parities][world + 1 sources][elems_per_src], 8 bytes each
-// A cell is written with ONE 8-byte store, so its reader sees value and epoch together: a cell
+// A cell is written with ONE 8-byte scalar store, so its reader sees value and epoch together: a cell
 // whose epoch equals the current call's is valid. No flag, no fence and no barrier is needed
 // between writer and reader. cells[p] is the base of rank p's buffer (p == rank: the local one).
 // Sources 0..world-1 hold the partial sums of those ranks; source `world` holds finished sums
@@ -84,14 +84,18 @@ __device__ __forceinline__ void stamp(const GemmParams& p, int slot) {
 
 
 // ---------------------------------------------------------------- cross-GPU exchange (row-parallel)
+// A cell is ONE 64-bit scalar access: value in the low word, epoch in the high word. A scalar access
+// of eight aligned bytes is single-copy atomic, so a reader never sees the new epoch beside an old
+// value (the two halves of a vector access carry no such promise).
 __device__ __forceinline__ void st_relaxed_sys_v2(uint2* ptr, uint32_t x, uint32_t y) {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(x), "r"(y) : "memory");
+    const unsigned long long cell = (static_cast<unsigned long long>(y) << 32) | x;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ptr), "l"(cell) : "memory");
 }
 
 __device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* ptr) {
-    uint2 v;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
-    return v;
+    unsigned long long cell;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(cell) : "l"(ptr) : "memory");
+    return make_uint2(static_cast<uint32_t>(cell), static_cast<uint32_t>(cell >> 32));
 }
 
 // All-reduce of the values this thread owns, fused into the GEMM epilogue. `val` holds CNT partial

@@ -236,7 +236,7 @@ constexpr BuiltinShape kBuiltinShapes[] = {
 //     computes 128 lanes per tile; the lanes past the tile's rows are ignored. The height stays a
 //     multiple of 8 so that the epilogue's 16-byte stores stay aligned.
 int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int stages_req, Plan* plan,
-              int tile_rows_req = 0) {
+              int tile_rows_req = 0, int max_per_sm = kModelMaxPerSm) {
     if (m <= 0 || n <= 0 || k <= 0 || m > kMaxMPad) return HFRK_INVALID_CONFIG;
     if (tile_rows_req < kAutoTileRowsOff || tile_rows_req > kTileN || (tile_rows_req > 0 && tile_rows_req < 8))
         return HFRK_INVALID_CONFIG;
@@ -252,7 +252,7 @@ int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int sta
     auto resident = [&](int split, int stages) {
         const int smem = plan_smem_bytes(m, m_pad, split, stages);
         if (smem > kSmemLimit) return false;
-        const int per_sm = ctas_per_sm(smem);
+        const int per_sm = ctas_per_sm(smem) < max_per_sm ? ctas_per_sm(smem) : max_per_sm;
         // one cluster to spare: at the exact capacity a straggler of the previous grid keeps the last one out
         return per_sm >= 1 && tiles < dm.capacity[split][per_sm];
     };
@@ -278,7 +278,8 @@ int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int sta
     if (split == 0) {
         split = 1;
         if (tiles < dm.sms) {
-            // largest resident split, three CTAs per SM first (a short ring), then two
+            // largest resident split; a ring of three stages lets three CTAs share an SM, four stages
+            // two. More CTAs win; with equal CTAs the longer ring does.
             int best_ctas = 0;
             const int ring_choices[2] = {3, 4};
             for (int choice = 0; choice < 2; ++choice) {
@@ -286,7 +287,7 @@ int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int sta
                 for (int s = kMaxSplit; s >= 2; --s) {
                     if (nkb / s < 2) continue;
                     if (!resident(s, ring)) continue;
-                    if (tiles * s > best_ctas) {
+                    if (tiles * s >= best_ctas) {
                         best_ctas = tiles * s;
                         split = s;
                         if (stages_req == 0) stages = ring;
@@ -574,7 +575,9 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         Plan plan;
         // the exchange buffer of the row-parallel kernel is laid out in 128-row tiles
         rc = make_plan(device_model(stream), mc, n, k, split_req, stages_req, &plan,
-                       rowpar != nullptr ? kAutoTileRowsOff : tile_rows_req);
+                       rowpar != nullptr ? kAutoTileRowsOff : tile_rows_req,
+                       // the row-parallel instantiation keeps the exchange in registers: two CTAs per SM
+                       rowpar != nullptr ? 2 : kModelMaxPerSm);
         if (rc != HFRK_SUCCESS) return rc;
         CUtensorMap tmap_w;
         rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
