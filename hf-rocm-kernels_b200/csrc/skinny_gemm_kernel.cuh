@@ -114,15 +114,19 @@ __device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* ptr) {
 //
 // Either way all ranks end with bit-identical sums. Nothing here synchronises the CTA; every wait
 // is bounded. Returns false if a peer did not deliver in time (the status word is set).
-template <int CNT>
-__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
+template <int CNT, int WORLD>
+__device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
                                                 float (&val)[CNT], volatile uint32_t* abort_flag) {
+    // WORLD > 0: the group size is known at compile time, so the loops over the ranks unroll to exactly
+    // that many cells; WORLD == 0 is the general form (any size up to kMaxWorld).
+    constexpr int kSrcs = WORLD > 0 ? WORLD : kMaxWorld;
+    const int world = WORLD > 0 ? WORLD : rp.world;
     const unsigned int parity = epoch & 1u;
-    const size_t sources = static_cast<size_t>(rp.world) + 1;
-    const int owner = rp.two_shot ? static_cast<int>((blockIdx.x + blockIdx.y) % static_cast<unsigned>(rp.world)) : -1;
+    const size_t sources = static_cast<size_t>(world) + 1;
+    const int owner = rp.two_shot ? static_cast<int>((blockIdx.x + blockIdx.y) % static_cast<unsigned>(world)) : -1;
     const bool gather = !rp.two_shot || owner == rp.rank;   // this thread adds up the ranks' partials
     const size_t my_src = parity * sources + static_cast<size_t>(rp.rank);
-    for (int peer = 0; peer < rp.world; ++peer) {
+    for (int peer = 0; peer < world; ++peer) {
         if (peer == rp.rank || (rp.two_shot && peer != owner)) continue;
         uint2* dst = rp.cells[peer] + my_src * rp.elems_per_src;
 #pragma unroll
@@ -144,15 +148,15 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
         for (int b = 0; b < kBatch; ++b) any |= slot[i0 + b] != 0xffffffffu;
         if (!any || !ok) continue;
         if (gather) {
-            uint32_t got[kBatch][kMaxWorld];
+            uint32_t got[kBatch][kSrcs];
             for (;;) {
                 bool ready = true;
 #pragma unroll
                 for (int b = 0; b < kBatch; ++b) {
 #pragma unroll
-                    for (int src = 0; src < kMaxWorld; ++src) {
+                    for (int src = 0; src < kSrcs; ++src) {
                         got[b][src] = 0u;
-                        if (src < rp.world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
+                        if (src < world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
                             const uint2 cell =
                                 ld_relaxed_sys_v2(mine + static_cast<size_t>(src) * rp.elems_per_src + slot[i0 + b]);
                             got[b][src] = cell.x;
@@ -173,15 +177,15 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
             for (int b = 0; b < kBatch; ++b) {
                 float sum = 0.0f;
 #pragma unroll
-                for (int src = 0; src < kMaxWorld; ++src) {
-                    if (src < rp.world) sum += (src == rp.rank) ? val[i0 + b] : __uint_as_float(got[b][src]);
+                for (int src = 0; src < kSrcs; ++src) {
+                    if (src < world) sum += (src == rp.rank) ? val[i0 + b] : __uint_as_float(got[b][src]);
                 }
                 val[i0 + b] = sum;
             }
             if (rp.two_shot) {
                 // the owner hands the finished sums to everyone else
-                const size_t fin = (parity * sources + static_cast<size_t>(rp.world)) * rp.elems_per_src;
-                for (int peer = 0; peer < rp.world; ++peer) {
+                const size_t fin = (parity * sources + static_cast<size_t>(world)) * rp.elems_per_src;
+                for (int peer = 0; peer < world; ++peer) {
                     if (peer == rp.rank) continue;
 #pragma unroll
                     for (int b = 0; b < kBatch; ++b) {
@@ -192,7 +196,7 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
             }
         } else {
             // not the owner: wait for the finished sums
-            const uint2* const fin = mine + static_cast<size_t>(rp.world) * rp.elems_per_src;
+            const uint2* const fin = mine + static_cast<size_t>(world) * rp.elems_per_src;
             uint32_t got[kBatch];
             for (;;) {
                 bool ready = true;
@@ -221,6 +225,20 @@ __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned in
         }
     }
     return ok;
+}
+
+// The exchange for the group sizes that matter (2, 4 and 8 GPUs) is compiled for its size: the
+// epilogue threads run alone on their schedulers, and the general form's loops over eight possible
+// ranks, most of them predicated off, cost microseconds of issue time per call.
+template <int CNT>
+__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
+                                                float (&val)[CNT], volatile uint32_t* abort_flag) {
+    switch (rp.world) {
+        case 2: return rowpar_exchange_impl<CNT, 2>(rp, epoch, slot, val, abort_flag);
+        case 4: return rowpar_exchange_impl<CNT, 4>(rp, epoch, slot, val, abort_flag);
+        case 8: return rowpar_exchange_impl<CNT, 8>(rp, epoch, slot, val, abort_flag);
+        default: return rowpar_exchange_impl<CNT, 0>(rp, epoch, slot, val, abort_flag);
+    }
 }
 
 // Instantiations of the kernel.
@@ -416,7 +434,22 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
     const bool lane_valid = tid < lim_cols;
     const int rpo = 1 << p.rows_log2;
     unsigned int epoch = 0;
-    if (kRowPar) epoch = *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
+    if (kRowPar) {
+        epoch = *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
+        if (tid == 0) {
+            // Once every CTA of the grid has read the call index it may move on: the last CTA to
+            // say so closes the call. The count is taken here, not at the end of the kernel, so
+            // that the round trip is hidden behind the wait for the accumulator; its operand is
+            // derived from the loaded index, so the load is performed before the count is.
+            unsigned int one;
+            asm volatile("{\n\t.reg .u32 t;\n\tand.b32 t, %1, 0;\n\tadd.u32 %0, t, 1;\n\t}" : "=r"(one) : "r"(epoch));
+            const unsigned int ctas = gridDim.x * gridDim.y;
+            if (atomicAdd(p.rp.done_ctas, one) == ctas - 1u) {
+                *p.rp.done_ctas = 0u;
+                *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) = epoch;
+            }
+        }
+    }
     const uint32_t tile_slot0 = blockIdx.x * static_cast<uint32_t>(p.m * kTileN);
 
     // D_in of this thread's first work item, requested long before it is needed.
@@ -926,17 +959,6 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kMmaWarp) tmem_dealloc(tmem_acc, tmem_cols);
-    if (kMode == kModeRowPar && threadIdx.x == 0) {
-        // The last CTA of the grid closes the call: every CTA has read the call index by now.
-        __threadfence();
-        const unsigned int ctas = gridDim.x * gridDim.y;
-        if (atomicAdd(p.rp.done_ctas, 1u) == ctas - 1u) {
-            *p.rp.done_ctas = 0u;
-            *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) =
-                *reinterpret_cast<volatile unsigned int*>(p.rp.call_index) + 1u;
-            __threadfence();
-        }
-    }
     if (threadIdx.x == 0) stamp(p, 7);
 }
 

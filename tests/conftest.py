@@ -59,3 +59,17 @@ def c_oracle(oracle_mod):
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With HFRK_PARITY_SUMMARY=<path>: one JSON line per parity case that the GPU tests checked
+    (elements, how many lie beyond the stated bound, how many beyond bound + floor, worst ratio)."""
+    path = os.environ.get("HFRK_PARITY_SUMMARY")
+    module = sys.modules.get("test_gpu_parity")
+    if not path or module is None or not getattr(module, "PARITY_ROWS", None):
+        return
+    import json
+
+    with open(path, "w") as fh:
+        for row in module.PARITY_ROWS:
+            fh.write(json.dumps(row) + "\n")

@@ -73,9 +73,12 @@ def main() -> None:
     c_oracle = oracle.load_c_oracle()
     c_oracle.set_threads(max(1, len(os.sched_getaffinity(0)) // world))
 
-    shapes = [wl.Case(3, 100, "down_m8", 8, 8192, 28672), wl.Case(3, 101, "down_m16_bias", 16, 8192, 28672, bias=True),
-              wl.Case(3, 102, "small_m3", 3, 1000, 2048 * world), wl.Case(3, 103, "wide_m1", 1, 20480, 1024 * world),
-              wl.Case(3, 104, "m40", 40, 1024, 512 * world, bias=True)]
+    # the benchmark's row-parallel configuration exactly (M in {1,2,8,16}, N=8192, K=28672), then shapes
+    # that reach the other code paths: a bias, ragged N, one token on a wide matrix, more than 16 tokens
+    shapes = wl.cases(3) + [wl.Case(3, 101, "down_m16_bias", 16, 8192, 28672, bias=True),
+                            wl.Case(3, 102, "small_m3", 3, 1000, 2048 * world),
+                            wl.Case(3, 103, "wide_m1", 1, 20480, 1024 * world),
+                            wl.Case(3, 104, "m40", 40, 1024, 512 * world, bias=True)]
     group = RowParallelSkinnyGemm(max_m=64, max_n=20480)
     for case in shapes:
         inp = wl.make_inputs(case, device="cpu")
@@ -106,7 +109,7 @@ def main() -> None:
         for out in outs:
             res = oracle.compare(out.float().cpu().numpy(), ref, case.k, scale, oracle.BF16, floor)
             assert res["hard_violations"] == 0 and res["nan_out"] == 0, (rank, case.name, res)
-            assert res["violations"] <= max(2, 2e-4 * res["count"]), (rank, case.name, res)
+            assert res["violations"] <= oracle.strict_exception_cap(case.k), (rank, case.name, res)
             assert torch.equal(out, outs[0])
         # every rank holds the same bits
         gathered = [torch.empty_like(outs[0]) for _ in range(world)]

@@ -4,8 +4,11 @@ and through the torch op. Everything here needs a B200.
 Criterion (per element, ``ref`` = the oracle's float32 value, exact accumulation):
     |out - ref| <= 1 ulp of the output dtype at ref + 1e-3 * sqrt(K) * |scale|
 For outputs that land within ~1e-3 of zero this bound drops below what ANY fp32 accumulation of K
-signed products can guarantee, so such elements are allowed the accumulation floor of
-``oracle.accumulation_floor`` on top, and their number is bounded (a few per 100k outputs).
+signed products can guarantee (tests/test_oracle_golden.py shows a host float32 matmul breaking it
+in two summation orders), so such elements are allowed the accumulation floor of
+``oracle.accumulation_floor`` on top; their number is capped at ``oracle.strict_exception_cap(K)``:
+none up to K = 8192, at most 8 per case beyond. With HFRK_PARITY_SUMMARY=<path> in the environment
+the per-case counts are written to that file as JSON lines.
 """
 import math
 
@@ -15,7 +18,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-MAX_SOFT_VIOLATION_RATE = 2e-4   # share of elements that may need the accumulation floor
+PARITY_ROWS = []   # one entry per checked case; written out by conftest when HFRK_PARITY_SUMMARY is set
 
 
 @pytest.fixture(scope="module")
@@ -50,7 +53,10 @@ def checker(oracle_mod, c_oracle):
             oracle_mod.kind_factor(a_kind, w_kind)), d_kind, floor)
         assert res["nan_out"] == 0, (label, res)
         assert res["hard_violations"] == 0, (label, res)
-        assert res["violations"] <= max(2, MAX_SOFT_VIOLATION_RATE * res["count"]), (label, res)
+        PARITY_ROWS.append({"case": label, "k": int(a_q.shape[1]), "count": res["count"],
+                            "beyond_stated_bound": res["violations"], "beyond_bound_plus_floor": res["hard_violations"],
+                            "worst_err_over_bound": round(res["max_err_over_tol"], 3)})
+        assert res["violations"] <= oracle_mod.strict_exception_cap(a_q.shape[1]), (label, res)
         return ref
 
     return check
@@ -97,7 +103,7 @@ def test_config1_llama3_8b(capi, dev, checker, index):
     checker(out, a, w, scale, d_in, case.name)
 
 
-@pytest.mark.parametrize("index", [0, 1, 3, 5, 8, 9, 10, 11])
+@pytest.mark.parametrize("index", range(12))
 def test_config2_llama3_70b_whole_matrices(capi, dev, checker, index):
     from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
 
