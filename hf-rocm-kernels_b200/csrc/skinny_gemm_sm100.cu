@@ -1103,6 +1103,199 @@ int host_call(const void* A_host, const void* W_dev, void* D_host, const float* 
 }  // namespace
 }  // namespace hfrk
 
+// =============================================================================== host batch
+namespace hfrk {
+namespace {
+
+constexpr size_t kBatchMergeBytes = 512 * 1024;   // largest merged activation copy; smallest result group
+constexpr int kBatchEvents = 64;
+
+// Per device: the library's copy stream and a ring of events (an event may be recorded again while
+// an older wait on it is pending: a wait refers to the record that preceded it).
+struct BatchResources {
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t events[kBatchEvents] = {};
+    int next_event = 0;
+    bool ready = false;
+};
+std::mutex g_batch_mutex;
+BatchResources g_batch[64];
+
+int batch_resources(BatchResources** out) {
+    int dev = 0;
+    HFRK_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return HFRK_INVALID_CONFIG;
+    BatchResources& r = g_batch[dev];
+    if (!r.ready) {
+        HFRK_CUDA_TRY(cudaStreamCreateWithFlags(&r.copy_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < kBatchEvents; ++i) {
+            HFRK_CUDA_TRY(cudaEventCreateWithFlags(&r.events[i], cudaEventDisableTiming));
+        }
+        r.ready = true;
+    }
+    *out = &r;
+    return HFRK_SUCCESS;
+}
+
+size_t out_elem_bytes(int d_dtype) { return d_dtype == HFRK_F32 ? 4 : 2; }
+size_t align16(size_t v) { return (v + 15) & ~static_cast<size_t>(15); }
+
+bool batch_call_valid(const hfrk_host_call& c) {
+    return c.A_host != nullptr && c.W_dev != nullptr && c.D_host != nullptr && c.scale_dev != nullptr && c.m > 0 &&
+           c.n > 0 && c.k > 0 && (c.d_dtype == HFRK_F16 || c.d_dtype == HFRK_BF16 || c.d_dtype == HFRK_F32);
+}
+
+}  // namespace
+}  // namespace hfrk
+
+extern "C" int64_t hfrk_host_batch_workspace_bytes(const hfrk_host_call* calls, int count) {
+    if (calls == nullptr || count <= 0) return 0;
+    size_t total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!hfrk::batch_call_valid(calls[i])) return 0;
+        // activations are packed as on the host (k % 16 == 0 keeps every block 16-byte aligned); outputs padded to 16
+        total += hfrk::align16(static_cast<size_t>(calls[i].m) * calls[i].k);
+        total += hfrk::align16(static_cast<size_t>(calls[i].m) * calls[i].n * hfrk::out_elem_bytes(calls[i].d_dtype));
+    }
+    return static_cast<int64_t>(total + 256);
+}
+
+extern "C" int hfrk_skinny_gemm_fp8_host_batch(const hfrk_host_call* calls, int count, void* work_dev,
+                                               int64_t work_bytes, void* stream) {
+    using namespace hfrk;
+    if (calls == nullptr || count <= 0 || work_dev == nullptr) return HFRK_INVALID_CONFIG;
+    if (work_bytes < hfrk_host_batch_workspace_bytes(calls, count) || hfrk_host_batch_workspace_bytes(calls, count) == 0)
+        return HFRK_INVALID_CONFIG;
+    for (int i = 0; i < count; ++i) {
+        if (calls[i].k % 16 != 0) return HFRK_K_NOT_DIVISIBLE;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::lock_guard<std::mutex> lock(g_batch_mutex);
+    BatchResources* res = nullptr;
+    int rc = batch_resources(&res);
+    if (rc != HFRK_SUCCESS) return rc;
+    auto next_event = [&]() {
+        cudaEvent_t e = res->events[res->next_event];
+        res->next_event = (res->next_event + 1) % kBatchEvents;
+        return e;
+    };
+
+    // device layout: all activation blocks, then all output blocks
+    uint8_t* const base = static_cast<uint8_t*>(work_dev);
+    size_t a_total = 0;
+    for (int i = 0; i < count; ++i) a_total += align16(static_cast<size_t>(calls[i].m) * calls[i].k);
+    uint8_t* const d_base = base + ((a_total + 255) & ~static_cast<size_t>(255));
+
+    // activations: host-contiguous runs merged into copies of at most kBatchMergeBytes, on the copy
+    // stream; needs_event[i] = the event the compute stream waits for before call i (or none)
+    cudaEvent_t needs_event[1024] = {};
+    if (count > 1024) return HFRK_TOO_LARGE;
+    {
+        // the scratch may still be in use by what was queued on `stream` before (the previous batch)
+        cudaEvent_t before = next_event();
+        HFRK_CUDA_TRY(cudaEventRecord(before, s));
+        HFRK_CUDA_TRY(cudaStreamWaitEvent(res->copy_stream, before, 0));
+    }
+    {
+        size_t dev_off = 0;
+        int i = 0;
+        while (i < count) {
+            const uint8_t* host0 = static_cast<const uint8_t*>(calls[i].A_host);
+            size_t run = 0;
+            int j = i;
+            // the first block is kept small so that the first GEMM does not wait for the whole step's input
+            const size_t limit = i == 0 ? kBatchMergeBytes / 4 : kBatchMergeBytes;
+            while (j < count && run < limit) {
+                const size_t bytes = static_cast<size_t>(calls[j].m) * calls[j].k;   // a multiple of 16
+                if (static_cast<const uint8_t*>(calls[j].A_host) != host0 + run) break;
+                run += bytes;
+                ++j;
+            }
+            HFRK_CUDA_TRY(cudaMemcpyAsync(base + dev_off, host0, run, cudaMemcpyHostToDevice, res->copy_stream));
+            // D_in of the chunk's accumulating calls travels with it, so that nothing but kernels sits
+            // on the compute stream (a copy between two kernels would end their overlap)
+            for (int t = i; t < j; ++t) {
+                if (!calls[t].accumulate) continue;
+                size_t off = 0;
+                for (int u = 0; u < t; ++u)
+                    off += align16(static_cast<size_t>(calls[u].m) * calls[u].n * out_elem_bytes(calls[u].d_dtype));
+                HFRK_CUDA_TRY(cudaMemcpyAsync(d_base + off, calls[t].D_host,
+                                              static_cast<size_t>(calls[t].m) * calls[t].n * out_elem_bytes(calls[t].d_dtype),
+                                              cudaMemcpyHostToDevice, res->copy_stream));
+            }
+            cudaEvent_t e = next_event();
+            HFRK_CUDA_TRY(cudaEventRecord(e, res->copy_stream));
+            needs_event[i] = e;
+            dev_off += run;
+            i = j;
+        }
+    }
+
+    // results leave in about three groups: each group's copy overlaps the next group's GEMMs, and
+    // every group costs one dependency between the two streams
+    size_t out_total = 0;
+    for (int i = 0; i < count; ++i) out_total += static_cast<size_t>(calls[i].m) * calls[i].n * out_elem_bytes(calls[i].d_dtype);
+    const size_t group_target = out_total / 3 > kBatchMergeBytes ? out_total / 3 : kBatchMergeBytes;
+    size_t a_off = 0, d_off = 0;
+    size_t group_bytes = 0;
+    int group_first = 0;
+    size_t group_first_off = 0;
+    auto flush_group = [&](int last) -> int {
+        // results of calls group_first..last: wait for the last GEMM, then copy out on the copy stream,
+        // merging calls whose host blocks follow each other as their device blocks do
+        cudaEvent_t e = next_event();
+        HFRK_CUDA_TRY(cudaEventRecord(e, s));
+        HFRK_CUDA_TRY(cudaStreamWaitEvent(res->copy_stream, e, 0));
+        size_t off = group_first_off;
+        int i = group_first;
+        while (i <= last) {
+            uint8_t* host0 = static_cast<uint8_t*>(calls[i].D_host);
+            size_t run = 0, dev_run = 0;
+            int j = i;
+            while (j <= last) {
+                const size_t bytes = static_cast<size_t>(calls[j].m) * calls[j].n * out_elem_bytes(calls[j].d_dtype);
+                if (static_cast<uint8_t*>(calls[j].D_host) != host0 + run || run != dev_run) break;
+                run += bytes;
+                dev_run += align16(bytes);
+                ++j;
+            }
+            HFRK_CUDA_TRY(cudaMemcpyAsync(host0, d_base + off, run, cudaMemcpyDeviceToHost, res->copy_stream));
+            // device blocks are padded to 16 bytes: a run only continues while no padding intervened
+            for (int t = i; t < j; ++t)
+                off += align16(static_cast<size_t>(calls[t].m) * calls[t].n * out_elem_bytes(calls[t].d_dtype));
+            i = j;
+        }
+        return HFRK_SUCCESS;
+    };
+
+    for (int i = 0; i < count; ++i) {
+        const hfrk_host_call& c = calls[i];
+        const size_t a_bytes = static_cast<size_t>(c.m) * c.k;
+        const size_t d_bytes = static_cast<size_t>(c.m) * c.n * out_elem_bytes(c.d_dtype);
+        if (needs_event[i] != nullptr) HFRK_CUDA_TRY(cudaStreamWaitEvent(s, needs_event[i], 0));
+        rc = launch_gemm(base + a_off, c.W_dev, d_base + d_off, c.scale_dev, c.m, c.n, c.k, c.w_row_stride, c.a_kind,
+                         c.w_kind, c.d_dtype, c.accumulate, HFRK_VARIANT_AUTO, 0, 0, 0, default_use_pdl(), s);
+        if (rc != HFRK_SUCCESS) return rc;
+        if (group_bytes == 0) {
+            group_first = i;
+            group_first_off = d_off;
+        }
+        group_bytes += d_bytes;
+        a_off += a_bytes;
+        d_off += align16(d_bytes);
+        // also right before the last call: its result is all that is left to copy when the GEMMs end
+        if (group_bytes >= group_target || i >= count - 2) {
+            rc = flush_group(i);
+            if (rc != HFRK_SUCCESS) return rc;
+            group_bytes = 0;
+        }
+    }
+    cudaEvent_t done = next_event();
+    HFRK_CUDA_TRY(cudaEventRecord(done, res->copy_stream));
+    HFRK_CUDA_TRY(cudaStreamWaitEvent(s, done, 0));
+    return HFRK_SUCCESS;
+}
+
 extern "C" int hfrk_skinny_gemm_plan(int m, int n, int k, int variant, int split_k, int ctas_per_sm, int* out8) {
     if (out8 == nullptr || variant < HFRK_VARIANT_AUTO || variant > HFRK_VARIANT_STREAMK) return HFRK_INVALID_CONFIG;
     const int mc = m > hfrk::kMaxMPad ? hfrk::kMaxMPad : m;

@@ -106,7 +106,20 @@ def _load() -> ctypes.CDLL:
     return lib
 
 
+class HostCall(ctypes.Structure):
+    """``hfrk_host_call`` of the header: one entry of a batch of host-buffer GEMM calls."""
+    _fields_ = [("A_host", ctypes.c_void_p), ("W_dev", ctypes.c_void_p), ("D_host", ctypes.c_void_p),
+                ("scale_dev", ctypes.c_void_p), ("m", ctypes.c_int), ("n", ctypes.c_int), ("k", ctypes.c_int),
+                ("w_row_stride", ctypes.c_int64), ("a_kind", ctypes.c_int), ("w_kind", ctypes.c_int),
+                ("d_dtype", ctypes.c_int), ("accumulate", ctypes.c_int)]
+
+
 lib = _load()
+lib.hfrk_host_batch_workspace_bytes.argtypes = [ctypes.POINTER(HostCall), ctypes.c_int]
+lib.hfrk_host_batch_workspace_bytes.restype = ctypes.c_int64
+lib.hfrk_skinny_gemm_fp8_host_batch.argtypes = [ctypes.POINTER(HostCall), ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
+                                                ctypes.c_void_p]
+lib.hfrk_skinny_gemm_fp8_host_batch.restype = ctypes.c_int
 
 
 class HfrkError(RuntimeError):
@@ -223,6 +236,35 @@ def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True
             a_host.data_ptr(), w_dev.data_ptr(), d_host.data_ptr(), scale_dev.data_ptr(), m, n, k, w_dev.stride(0),
             fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype), out_kind(d_host.dtype), int(accumulate),
             work_dev.data_ptr(), _stream_ptr(stream, w_dev.device))
+
+
+class HostBatch:
+    """A fixed list of host-buffer GEMM calls, prepared once and queued with one library call per
+    step (``hfrk_skinny_gemm_fp8_host_batch``). ``calls`` = [(a_host, w_dev, d_host, scale_dev, accumulate)];
+    the tensors must outlive the object, the host ones should be page-locked."""
+
+    def __init__(self, calls, device: torch.device):
+        self.device = device
+        self.array = (HostCall * len(calls))()
+        self.keep = list(calls)
+        for slot, (a_host, w_dev, d_host, scale_dev, accumulate) in zip(self.array, calls):
+            m, k = a_host.shape
+            n = w_dev.shape[0]
+            assert a_host.device.type == "cpu" and d_host.device.type == "cpu" and w_dev.stride(1) == 1
+            assert a_host.is_contiguous() and d_host.is_contiguous() and tuple(d_host.shape) == (m, n)
+            slot.A_host, slot.W_dev, slot.D_host = a_host.data_ptr(), w_dev.data_ptr(), d_host.data_ptr()
+            slot.scale_dev, slot.m, slot.n, slot.k = scale_dev.data_ptr(), m, n, k
+            slot.w_row_stride, slot.a_kind, slot.w_kind = w_dev.stride(0), fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype)
+            slot.d_dtype, slot.accumulate = out_kind(d_host.dtype), int(accumulate)
+        self.work_bytes = lib.hfrk_host_batch_workspace_bytes(self.array, len(calls))
+        assert self.work_bytes > 0, "invalid call in the batch"
+        self.work = torch.empty(self.work_bytes, dtype=torch.uint8, device=device)
+
+    def queue(self, stream: Optional[torch.cuda.Stream] = None) -> int:
+        """Queues the whole batch; results are in the host buffers once ``stream`` is synchronised."""
+        with _on_device(self.device):
+            return lib.hfrk_skinny_gemm_fp8_host_batch(self.array, len(self.array), self.work.data_ptr(), self.work_bytes,
+                                                       _stream_ptr(stream, self.device))
 
 
 def swiglu(gate_up: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, next_buffer: Optional[torch.Tensor] = None,

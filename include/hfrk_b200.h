@@ -123,6 +123,37 @@ int hfrk_skinny_gemm_fp8_host_async(const void* A_host, const void* W_dev, void*
                                     int a_kind, int w_kind, int d_dtype, int accumulate,
                                     void* work_dev, void* stream);
 
+/* One decode step's worth of host-buffer calls in ONE library call. A caller that drives the GEMMs
+ * one by one from an interpreter pays more for submitting a call than the GPU needs to run it; here
+ * the whole list is queued by one native loop:
+ *   * activations go host->device on a copy stream owned by the library, neighbouring host blocks
+ *     merged into copies of up to 512 KiB (one cudaMemcpyAsync per merged block, D_in of the
+ *     block's accumulating calls behind it), each followed by an event that `stream` waits for
+ *     only before the first GEMM that needs it;
+ *   * nothing but the GEMMs runs on `stream`, in list order, so consecutive calls overlap as they
+ *     do for device-resident callers;
+ *   * results go device->host on the copy stream in about three groups, each behind an event
+ *     recorded after the group's last GEMM, so that a group's copy overlaps the next group's GEMMs;
+ *   * `stream` finally waits for the last copy: the caller synchronises `stream` once and finds
+ *     every D_host filled.
+ * work_dev: device scratch of at least hfrk_host_batch_workspace_bytes(calls, count) bytes; host
+ * buffers should be page-locked (pageable ones make the copies synchronous, still correct) and
+ * must stay untouched until `stream` has been synchronised. Returns the first failing call's
+ * status. No counterpart in the reference, whose callers hold activations in CUDA tensors
+ * (hf_rocm_kernels/operators/skinny_gemm/wrapped.py:104-128). */
+typedef struct hfrk_host_call {
+    const void* A_host;      /* [m, k] fp8 */
+    const void* W_dev;       /* [n, k] fp8 on the device, row pitch w_row_stride */
+    void* D_host;            /* [m, n] in/out */
+    const float* scale_dev;
+    int m, n, k;
+    int64_t w_row_stride;
+    int a_kind, w_kind, d_dtype, accumulate;
+} hfrk_host_call;
+int64_t hfrk_host_batch_workspace_bytes(const hfrk_host_call* calls, int count);
+int hfrk_skinny_gemm_fp8_host_batch(const hfrk_host_call* calls, int count, void* work_dev,
+                                    int64_t work_bytes, void* stream);
+
 /* ---- row-parallel (K split over GPUs) GEMM with the all-reduce fused into its epilogue ---------
  * Rank r of `world` holds columns [r*K/world, (r+1)*K/world) of A and W. Every rank calls
  * hfrk_skinny_gemm_fp8_rowpar with its shard; every rank ends with the full

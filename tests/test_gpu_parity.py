@@ -7,7 +7,7 @@ For outputs that land within ~1e-3 of zero this bound drops below what ANY fp32 
 signed products can guarantee (tests/test_oracle_golden.py shows a host float32 matmul breaking it
 in two summation orders), so such elements are allowed the accumulation floor of
 ``oracle.accumulation_floor`` on top; their number is capped at ``oracle.strict_exception_cap(K)``:
-none up to K = 8192, at most 8 per case beyond. With HFRK_PARITY_SUMMARY=<path> in the environment
+none up to K = 5120, at most 8 per case beyond. With HFRK_PARITY_SUMMARY=<path> in the environment
 the per-case counts are written to that file as JSON lines.
 """
 import math
@@ -312,6 +312,54 @@ def test_simt_diagnostic_kernel_agrees(capi, dev, checker):
     capi.check(capi.skinny_gemm_simt(a, w, out, s))
     torch.cuda.synchronize()
     checker(out, a, w, scale, d_in, "simt")
+
+
+@pytest.mark.parametrize("pinned,packed", [(True, True), (True, False), (False, False)])
+def test_host_batch_equals_the_device_calls(capi, dev, pinned, packed):
+    """hfrk_skinny_gemm_fp8_host_batch: a list of host-buffer calls queued by one library call gives,
+    bit for bit, what the same calls give one by one on device-resident tensors; with activations
+    and outputs packed in one host block each (merged copies), scattered, and in pageable memory;
+    twice in a row on the same scratch."""
+    shapes = [(16, 6144, 4096, True), (1, 4096, 4096, False), (5, 1000, 1040, True), (16, 28672, 4096, False),
+              (3, 4104, 5120, False), (13, 4096, 14336, True), (33, 1024, 2048, False)]
+    gen = torch.Generator().manual_seed(321)
+    a_block = torch.empty(sum(m * k for m, n, k, b in shapes), dtype=torch.uint8)
+    d_block = torch.empty(sum(m * n for m, n, k, b in shapes), dtype=torch.bfloat16)
+    if pinned:
+        a_block, d_block = a_block.pin_memory(), d_block.pin_memory()
+    calls, expect, a_off, d_off = [], [], 0, 0
+    for (m, n, k, bias) in shapes:
+        a = torch.randint(0, 120, (m, k), dtype=torch.uint8, generator=gen)
+        w = torch.randint(0, 120, (n, k), dtype=torch.uint8, generator=gen).view(torch.float8_e4m3fn).to(dev)
+        d0 = (torch.randn((m, n), generator=gen) if bias else torch.zeros((m, n))).bfloat16()
+        scale = torch.tensor([2e-4], device=dev)
+        if packed:
+            a_host = a_block[a_off:a_off + m * k].view(m, k)
+            d_host = d_block[d_off:d_off + m * n].view(m, n)
+        else:
+            a_host, d_host = torch.empty((m, k), dtype=torch.uint8), torch.empty((m, n), dtype=torch.bfloat16)
+            if pinned:
+                a_host, d_host = a_host.pin_memory(), d_host.pin_memory()
+        a_off, d_off = a_off + m * k, d_off + m * n
+        a_host.copy_(a)
+        d_host.copy_(d0)
+        want = d0.to(dev).clone()
+        capi.check(capi.skinny_gemm(a.view(torch.float8_e4m3fn).to(dev), w, want, scale, accumulate=bias))
+        calls.append((a_host.view(torch.float8_e4m3fn), w, d_host, scale, bias))
+        expect.append((want, d0))
+    torch.cuda.synchronize()
+    batch = capi.HostBatch(calls, dev)
+    stream = torch.cuda.Stream()
+    for _ in range(2):
+        for (a_host, w, d_host, scale, bias), (want, d0) in zip(calls, expect):
+            d_host.copy_(d0)
+        capi.check(batch.queue(stream))
+        stream.synchronize()
+        for (a_host, w, d_host, scale, bias), (want, d0) in zip(calls, expect):
+            assert torch.equal(d_host, want.cpu())
+    assert capi.device_status(clear=True)[0] == 0
+    # too little scratch and an invalid entry are refused
+    assert capi.lib.hfrk_skinny_gemm_fp8_host_batch(batch.array, len(calls), batch.work.data_ptr(), 1024, 0) == 6
 
 
 def test_host_buffer_entry_point(capi, dev, checker):

@@ -64,4 +64,5 @@ def test_a_peer_that_never_delivers_ends_the_call_with_a_status(native_build, mo
     capi.check(capi.skinny_gemm_simt(a, w, check, scale))
     torch.cuda.synchronize()
     assert capi.device_status(clear=True)[0] == 0
-    assert float((out.float() - check.float()).abs().max()) <= 0.26
+    # both kernels round to bf16: one step apart at most (a step is 2**-7 of the value)
+    assert bool(((out.float() - check.float()).abs() <= check.float().abs() * 2.0 ** -7 + 1e-3).all())
