@@ -163,7 +163,7 @@ def self_check(items, capi, wl, torch, dev):
     ref = oracle.load_c_oracle().skinny_gemm(a_q, w_q, scale, inp["d_in"].float().numpy())
     res = oracle.compare(out.float().cpu().numpy(), ref, case.k, scale, oracle.BF16,
                          oracle.accumulation_floor(a_q, w_q, scale))
-    if res["hard_violations"] or res["nan_out"] or res["violations"] > oracle.strict_exception_cap(case.k):
+    if res["hard_violations"] or res["nan_out"] or res["violations"] > oracle.strict_exception_cap(case.k, res["count"]):
         raise RuntimeError(f"self-check against the oracle failed on {case.name}: {res}")
     summary = {"oracle_case": case.name, "count": res["count"], "beyond_stated_bound": res["violations"],
                "beyond_bound_plus_floor": res["hard_violations"], "max_err_over_tol": round(res["max_err_over_tol"], 3)}
@@ -304,9 +304,21 @@ def run_ours(args):
             graph.replay()
         e1.record(stream)
         e1.synchronize()
-        barrier()
         device_ms = e0.elapsed_time(e1)
+        # K steps of ~0.23 ms are over before the sampler (one NVML query per ~2 ms) has seen much: the
+        # same graph keeps running, untimed, until the clock record covers at least 60 ms of this load
+        extra_replays = 0
+        if rank == 0:
+            window_start = time.perf_counter()
+            while time.perf_counter() - window_start < 0.06:
+                for _ in range(10):
+                    graph.replay()
+                stream.synchronize()
+                extra_replays += 10
+        barrier()
         clocks = sampler.stop() if rank == 0 else None
+        if clocks is not None:
+            clocks["window"] = f"the timed region plus {extra_replays} further replays of the same graph (same load, untimed)"
 
     # ---- the end-to-end leg: host buffers through the C ABI, copies inside the timed region. A step
     # hands its 20 calls to the library in ONE call (hfrk_skinny_gemm_fp8_host_batch): activations and
@@ -552,7 +564,7 @@ def multi_gpu_parity(torch, dist, capi, wl, dev, rank, world):
             floor = oracle.accumulation_floor(a_q, w_q, scale)
             res = oracle.compare(out_full.float().cpu().numpy(), ref, case.k, scale, oracle.BF16, floor)
             ok = (res["hard_violations"] == 0 and res["nan_out"] == 0 and
-                  res["violations"] <= oracle.strict_exception_cap(case.k))
+                  res["violations"] <= oracle.strict_exception_cap(case.k, res["count"]))
             report["strict_bound_exceptions"] += res["violations"]
             if not ok:
                 print(f"multi-GPU parity: {label} failed: {res}", file=sys.stderr, flush=True)

@@ -1,5 +1,5 @@
 """Every benchmark command of the package runs to the end on a small case (so that the commands
-quoted in the docs and in ``profiles/`` keep working). Needs a B200; checks exit codes and that the
+quoted in the documentation keep working). Needs a B200; checks exit codes and that the
 expected table or JSON comes out, not the numbers."""
 import os
 import subprocess
