@@ -174,7 +174,9 @@ residual_rms_vec8_kernel(const T* __restrict__ input, T* __restrict__ residual, 
         const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight) + c);
         normalise_store_8<T, kOut>(sv, wv, normaliser, quant_factor, out_row, c);
     }
-    zero_range(next_buffer, buffer_bytes);
+    // only with fp8 output, as in the reference (residual_rms_dispatch.cu:33-43 passes no buffer otherwise):
+    // a 16-bit output does not feed a GEMM that accumulates into next_buffer
+    if (kOut != kOutSame) zero_range(next_buffer, buffer_bytes);
 }
 
 // Scalar path: any cols, any alignment.
@@ -214,7 +216,9 @@ residual_rms_scalar_kernel(const T* __restrict__ input, T* __restrict__ residual
             static_cast<uint8_t*>(output)[row * cols + c] = byte;
         }
     }
-    zero_range(next_buffer, buffer_bytes);
+    // only with fp8 output, as in the reference (residual_rms_dispatch.cu:33-43 passes no buffer otherwise):
+    // a 16-bit output does not feed a GEMM that accumulates into next_buffer
+    if (kOut != kOutSame) zero_range(next_buffer, buffer_bytes);
 }
 
 // CTA size. A hint that is a multiple of 32 is taken as it is. Otherwise one work item (a 16-byte

@@ -205,8 +205,11 @@ int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* group, const void* A_shard, const v
  * process exits -- and calls no cudaMalloc, cudaFree or any allocating routine, on any call.
  * Limits: m <= 16 and n <= 524,288, otherwise HFRK_TOO_LARGE (hfrk_last_error says why); the
  * caller still passes A, W, D and the scale. The first call on a device looks up the array's
- * device address (cudaGetSymbolAddress, with that device current), so make that first call
- * before any stream capture. All calls share the one array, which keeps what the last call left:
+ * device address (cudaGetSymbolAddress, with that device current) and, with CUDA's lazy module
+ * loading, is also the moment the driver loads the library's module onto that device, the array
+ * included: make that first call at start-up, before any stream capture and BEFORE the caller's own
+ * pools take the rest of HBM (or run with CUDA_MODULE_LOADING=EAGER), or it can fail for lack of
+ * the very memory the entry point promises not to ask for later. All calls share the one array, which keeps what the last call left:
  * the tile counters a call uses are cleared on `stream` before its kernel, partials are always
  * written before they are read; two calls that overlap on the GPU (different streams) race on it.
  * Plain launch (no programmatic dependent launch). It has no counterpart in the reference. */
@@ -270,7 +273,9 @@ int hfrk_swiglu_fp8(const void* gate_up, const float* scale_dev, void* out, void
 /* residual <- input + residual (in place, rounded to the 16-bit type);
  * output <- residual * rsqrt(mean(residual^2) + epsilon) * weight, written in the 16-bit type
  * (out_kind HFRK_OUT_SAME, scale_dev may be NULL) or divided by *scale_dev and written as fp8
- * (HFRK_OUT_E4M3FN / HFRK_OUT_E4M3FNUZ); next_buffer[rows, buffer_cols] (16-bit elements) <- 0.
+ * (HFRK_OUT_E4M3FN / HFRK_OUT_E4M3FNUZ); with fp8 output also next_buffer[rows, buffer_cols]
+ * (16-bit elements) <- 0. With 16-bit output next_buffer is left alone, as in the reference
+ * (residual_rms_dispatch.cu:33-43).
  *   input, residual [rows, cols], weight [cols]: fp16 or bf16 (dtype: enum hfrk_out_dtype)
  *   num_threads : CTA size, a multiple of 32 in [32, 1024]; anything else lets the library choose
  * One CTA per row. cols % 8 == 0 with 16-byte aligned tensors takes 16-byte loads; anything else

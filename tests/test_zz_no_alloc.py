@@ -51,10 +51,17 @@ def test_noalloc_entry_matches_the_ordinary_one_twice_in_a_row(capi, oracle_mod,
     tol = oracle_mod.tolerance(ref, k, scale, oracle_mod.BF16) + floor
 
     results = []
-    for _ in range(2):                                                  # two calls in a row share the array
-        out = d0.clone()
+    outs = [d0.clone() for _ in range(3)]                               # made before the memory is read
+    torch.cuda.synchronize()
+    for call in range(3):                                               # calls in a row share the array
+        out = outs[call]
+        free_before = torch.cuda.mem_get_info(dev)[0]
         capi.check(capi.skinny_gemm_noalloc(a, w, out, s))
         torch.cuda.synchronize()
+        if call > 0:
+            # past the first call on the device (which loads the module and looks up the array) a call
+            # allocates nothing: the device's free memory does not move across it
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         assert capi.device_status(clear=True)[0] == 0
         res = oracle_mod.compare(out.float().cpu().numpy(), ref, k, scale, oracle_mod.BF16, floor)
         assert res["hard_violations"] == 0 and res["nan_out"] == 0, res
@@ -72,3 +79,12 @@ def test_noalloc_entry_rejects_sizes_beyond_its_fixed_array(capi):
     s = torch.ones(1, device=dev)
     assert capi.skinny_gemm_noalloc(a, w, d, s) == 12                   # HFRK_TOO_LARGE: more than 16 tokens
     assert b"16 tokens" in capi.lib.hfrk_last_error()
+    # more than 4096 tiles of 128 rows (N > 524,288): the tile counters of the fixed array run out
+    n_big = 4097 * 128
+    a1 = torch.zeros((1, 16), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    w_big = torch.zeros((n_big, 16), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    d_big = torch.zeros((1, n_big), dtype=torch.bfloat16, device=dev)
+    assert capi.skinny_gemm_noalloc(a1, w_big, d_big, s) == 12
+    n_ok = 4096 * 128
+    assert capi.skinny_gemm_noalloc(a1, w_big[:n_ok], d_big[:, :n_ok].contiguous(), s) == 0
+    torch.cuda.synchronize()
