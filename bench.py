@@ -35,7 +35,7 @@ sys.path.insert(0, os.path.join(ROOT, "hf-rocm-kernels_b200"))
 METRIC = "fp8_skinny_gemm_hbm_bandwidth"
 UNIT = "TB/s"
 WORKLOAD = "llama3_8b_decode_projections_fp8_e4m3_bf16out_M1-16 (configuration 1)"
-L2_BYTES = 126 * 1024 * 1024
+L2_BYTES = 126 * 1024 * 1024   # B200; replaced by the device's own figure once a GPU is in hand (run_ours)
 
 
 def measured_hbm_peak_gbs():
@@ -267,6 +267,8 @@ def run_ours(args):
         raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    global L2_BYTES
+    L2_BYTES = int(torch.cuda.get_device_properties(dev).L2_cache_size)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 

@@ -229,16 +229,12 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
 
 // The exchange for the group sizes that matter (2, 4 and 8 GPUs) is compiled for its size: the
 // epilogue threads run alone on their schedulers, and the general form's loops over eight possible
-// ranks, most of them predicated off, cost microseconds of issue time per call.
-template <int CNT>
+// ranks, most of them predicated off, cost microseconds of issue time per call. kWorld = 0 is the
+// general form.
+template <int CNT, int kWorld>
 __device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
                                                 float (&val)[CNT], volatile uint32_t* abort_flag) {
-    switch (rp.world) {
-        case 2: return rowpar_exchange_impl<CNT, 2>(rp, epoch, slot, val, abort_flag);
-        case 4: return rowpar_exchange_impl<CNT, 4>(rp, epoch, slot, val, abort_flag);
-        case 8: return rowpar_exchange_impl<CNT, 8>(rp, epoch, slot, val, abort_flag);
-        default: return rowpar_exchange_impl<CNT, 0>(rp, epoch, slot, val, abort_flag);
-    }
+    return rowpar_exchange_impl<CNT, kWorld>(rp, epoch, slot, val, abort_flag);
 }
 
 // Instantiations of the kernel.
@@ -424,7 +420,7 @@ __device__ __forceinline__ bool wait_accumulator(const GemmParams& p, const EpiC
 //
 // With a K split every CTA sends its partial rows to their owners (send_partial_rows), an owner
 // waits for all `split` blocks and thread t adds up and stores column t of the owner's rows.
-template <int kMode, int DT>
+template <int kMode, int DT, int kWorld>
 __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx& cx) {
     constexpr bool kRowPar = kMode == kModeRowPar;
     const int tid = threadIdx.x;
@@ -491,7 +487,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
                     val[j] = __uint_as_float(v[j]);
                     slot[j] = j < p.m ? tile_slot0 + static_cast<uint32_t>(j * kTileN + tid) : 0xffffffffu;
                 }
-                if (!rowpar_exchange<16>(p.rp, epoch, slot, val, &cx.ctrl->abort)) ok = false;
+                if (!rowpar_exchange<16, kWorld>(p.rp, epoch, slot, val, &cx.ctrl->abort)) ok = false;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(val[j]);
             }
@@ -583,7 +579,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
             const int row = own_row0 + it;
             slot[it] = (it < rpo && row < p.m) ? tile_slot0 + static_cast<uint32_t>(row * kTileN + tid) : 0xffffffffu;
         }
-        if (!rowpar_exchange<kOwned>(p.rp, epoch, slot, own, &cx.ctrl->abort)) return;
+        if (!rowpar_exchange<kOwned, kWorld>(p.rp, epoch, slot, own, &cx.ctrl->abort)) return;
     }
     if (!lane_valid) return;
     {
@@ -746,7 +742,11 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const EpiCt
 #ifndef HFRK_MIN_CTAS
 #define HFRK_MIN_CTAS 2
 #endif
-template <int kMode>
+// kDT / kWorld: the plain and the gate/up kernel decide the output type at run time (kDT = -1); the
+// row-parallel kernel is instantiated per output type and group size (2, 4, 8, or 0 = any), because
+// one kernel holding every exchange variant needed 168 registers with spills and cost 2-3 us per
+// call more than the plain kernel even in a group of one.
+template <int kMode, int kDT = -1, int kWorld = 0>
 __global__ void __launch_bounds__(kThreads, HFRK_MIN_CTAS)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
@@ -944,13 +944,15 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
         cx.scale = __ldg(p.scale) * p.kind_factor;
         if constexpr (kMode == kModeSwiglu) {
             epilogue_swiglu(p, cx);
+        } else if constexpr (kDT >= 0) {
+            epilogue_store<kMode, kDT, kWorld>(p, cx);
         } else {
             if (p.d_dtype == HFRK_BF16) {
-                epilogue_store<kMode, HFRK_BF16>(p, cx);
+                epilogue_store<kMode, HFRK_BF16, kWorld>(p, cx);
             } else if (p.d_dtype == HFRK_F16) {
-                epilogue_store<kMode, HFRK_F16>(p, cx);
+                epilogue_store<kMode, HFRK_F16, kWorld>(p, cx);
             } else {
-                epilogue_store<kMode, HFRK_F32>(p, cx);
+                epilogue_store<kMode, HFRK_F32, kWorld>(p, cx);
             }
         }
     }

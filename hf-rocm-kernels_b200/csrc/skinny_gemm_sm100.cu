@@ -347,6 +347,25 @@ int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int sta
     return HFRK_SUCCESS;
 }
 
+// The row-parallel kernel for an output type and a group size (sizes other than 2, 4, 8 share the
+// general form).
+using GemmKernel = void (*)(const CUtensorMap, const CUtensorMap, const GemmParams);
+template <int kDT>
+GemmKernel rowpar_kernel_for_world(int world) {
+    switch (world) {
+        case 2: return skinny_gemm_fp8_sm100_kernel<kModeRowPar, kDT, 2>;
+        case 4: return skinny_gemm_fp8_sm100_kernel<kModeRowPar, kDT, 4>;
+        case 8: return skinny_gemm_fp8_sm100_kernel<kModeRowPar, kDT, 8>;
+        default: return skinny_gemm_fp8_sm100_kernel<kModeRowPar, kDT, 0>;
+    }
+}
+const void* rowpar_kernel(int d_dtype, int world) {
+    GemmKernel fn = d_dtype == HFRK_BF16 ? rowpar_kernel_for_world<HFRK_BF16>(world)
+                    : d_dtype == HFRK_F16 ? rowpar_kernel_for_world<HFRK_F16>(world)
+                                          : rowpar_kernel_for_world<HFRK_F32>(world);
+    return reinterpret_cast<const void*>(fn);
+}
+
 int prepare_device_once() {
     static std::mutex mu;
     static bool done[64] = {};
@@ -358,10 +377,13 @@ int prepare_device_once() {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModePlain>,
                                        cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeRowPar>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeRowPar>,
-                                       cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    for (int dt = 0; dt < 3; ++dt) {
+        for (int world : {0, 2, 4, 8}) {
+            const void* fn = rowpar_kernel(dt, world);
+            HFRK_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+            HFRK_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        }
+    }
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeSwiglu>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     HFRK_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_fp8_sm100_kernel<kModeSwiglu>,
@@ -643,7 +665,8 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         cfg.attrs = attrs;
         cfg.numAttrs = num_attrs;
         if (rowpar != nullptr) {
-            HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<kModeRowPar>, tmap_w, tmap_a, p));
+            void* args[3] = {&tmap_w, &tmap_a, &p};
+            HFRK_CUDA_TRY(cudaLaunchKernelExC(&cfg, rowpar_kernel(d_dtype, p.rp.world), args));
         } else {
             HFRK_CUDA_TRY(cudaLaunchKernelEx(&cfg, skinny_gemm_fp8_sm100_kernel<kModePlain>, tmap_w, tmap_a, p));
         }

@@ -7,6 +7,7 @@ alone. A graph holds ``graph_size`` calls, each on its own set of tensors so tha
 inputs in L1, and the figure returned is the median replay time divided by ``graph_size``.
 """
 import itertools
+import warnings
 from typing import Callable, Dict, Sequence
 
 import torch
@@ -58,7 +59,24 @@ class Bench:
 
     def __init__(self) -> None:
         torch.set_grad_enabled(False)
+        self.check_device_is_free(warn_if_not=True)
         self._measures: Dict[str, Dict[int, float]] = {}
+
+    @staticmethod
+    def check_device_is_free(warn_if_not: bool = False) -> Dict[str, int]:
+        """Utilisation and memory use of the current GPU as NVML reports them (read-only queries); on a
+        shared machine a busy GPU explains a bad number. Same role as the reference's
+        ``Bench.check_device_is_free`` (``utils/benchmarking.py:83-95``). Returns -1 where NVML is
+        not available."""
+        metrics = {"utilization": -1, "memory_usage": -1}
+        try:
+            metrics["utilization"] = int(torch.cuda.utilization())
+            metrics["memory_usage"] = int(torch.cuda.memory_usage())
+        except Exception:
+            pass
+        if warn_if_not and (metrics["utilization"] > 0 or metrics["memory_usage"] > 0):
+            warnings.warn(f"Device {torch.cuda.current_device()} is not fully free: {metrics = }")
+        return metrics
 
     @staticmethod
     def benchmark_fn(fn: Callable[[], None], graph_size: int = 16, iterations: int = 50) -> float:

@@ -58,3 +58,17 @@ def test_grid_search_writes_a_table_the_loader_accepts(native_build, tmp_path):
         assert tuning.load_tuning(str(out)) >= 1
     finally:
         tuning.clear_tuning()
+
+
+def test_general_timing_function_and_device_check(native_build):
+    """benchmark_skinny_gemm_general (the reference's hand-knob timing entry point) with the
+    operator and with torch._scaled_mm (split_k = 0), and Bench.check_device_is_free."""
+    from hf_rocm_kernels.operators.skinny_gemm.benchmarking_fn import benchmark_skinny_gemm_general
+    from hf_rocm_kernels.utils.benchmarking import Bench
+
+    ours, _ = benchmark_skinny_gemm_general(4, 1024, 1024, split_k=2, A_producers=1, B_producers=2, consumers=3,
+                                            a_lanes=1, b_lanes=2, qsize=3, op_m=8, ops=4, warmups=2, iterations=4)
+    vendor, _ = benchmark_skinny_gemm_general(16, 1024, 1024, split_k=0, warmups=2, iterations=4)
+    assert 0.5 < ours < 1000 and 0.5 < vendor < 1000
+    metrics = Bench.check_device_is_free()
+    assert set(metrics) == {"utilization", "memory_usage"}
