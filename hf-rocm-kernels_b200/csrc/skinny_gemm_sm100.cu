@@ -911,6 +911,7 @@ struct hfrk_rowpar {
     int device = 0;
     bool connected = false;
     int mode = HFRK_ROWPAR_AUTO;
+    unsigned long long* stamps = nullptr;   // diagnostic: per-CTA time stamps of the next calls
 };
 
 extern "C" int hfrk_rowpar_create(int rank, int world, int max_m, int max_n, hfrk_rowpar** out) {
@@ -997,13 +998,19 @@ extern "C" int hfrk_skinny_gemm_fp8_rowpar(hfrk_rowpar* g, const void* A, const 
     if (g == nullptr || !g->connected) return HFRK_BAD_WORLD;
     return hfrk::launch_gemm(A, W, D, scale_dev, m, n, k_shard, w_row_stride, a_kind, w_kind, d_dtype, accumulate,
                              HFRK_VARIANT_CLUSTER, 0, 0, 0, hfrk::default_use_pdl(), static_cast<cudaStream_t>(stream),
-                             nullptr, &g->dev, g->mode);
+                             g->stamps, &g->dev, g->mode);
 }
 
 extern "C" int hfrk_rowpar_set_wait_ms(hfrk_rowpar* g, int milliseconds) {
     if (g == nullptr) return HFRK_BAD_WORLD;
     if (milliseconds < 1 || milliseconds > 60000) return HFRK_INVALID_CONFIG;
     g->dev.wait_cycles = static_cast<long long>(milliseconds) * 2000000ll;   // SM clock ticks at ~2 GHz
+    return HFRK_SUCCESS;
+}
+
+extern "C" int hfrk_rowpar_set_stamps(hfrk_rowpar* g, unsigned long long* stamps_dev) {
+    if (g == nullptr) return HFRK_BAD_WORLD;
+    g->stamps = stamps_dev;
     return HFRK_SUCCESS;
 }
 

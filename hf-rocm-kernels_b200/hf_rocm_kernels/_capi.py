@@ -71,6 +71,8 @@ def _load() -> ctypes.CDLL:
     lib.hfrk_rowpar_set_wait_ms.argtypes = [vp, i32]
     lib.hfrk_rowpar_set_wait_ms.restype = i32
     lib.hfrk_rowpar_set_mode.restype = i32
+    lib.hfrk_rowpar_set_stamps.argtypes = [vp, vp]
+    lib.hfrk_rowpar_set_stamps.restype = i32
     lib.hfrk_skinny_gemm_fp8_rowpar.argtypes = [vp] + common + [vp]
     for name in ("hfrk_rowpar_create", "hfrk_rowpar_ipc_handle", "hfrk_rowpar_connect",
                  "hfrk_rowpar_connect_pointers", "hfrk_rowpar_destroy", "hfrk_skinny_gemm_fp8_rowpar"):

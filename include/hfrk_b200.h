@@ -187,6 +187,9 @@ int hfrk_rowpar_destroy(hfrk_rowpar* group);
  * 1 MiB. Every rank of the group must use the same mode for the same call. */
 enum hfrk_rowpar_mode { HFRK_ROWPAR_AUTO = 0, HFRK_ROWPAR_ONE_SHOT = 1, HFRK_ROWPAR_TWO_SHOT = 2 };
 int hfrk_rowpar_set_mode(hfrk_rowpar* group, int mode);
+/* Diagnostic: later calls of this group record per-CTA time stamps into stamps_dev[cta][8] as
+ * hfrk_skinny_gemm_fp8_profile does (NULL = off). No counterpart in the reference. */
+int hfrk_rowpar_set_stamps(hfrk_rowpar* group, unsigned long long* stamps_dev);
 /* How long the kernel waits for a peer's partial sums before it gives up, in milliseconds of SM
  * clock at ~2 GHz (1..60000; the default is about two seconds). A call whose peer does not
  * deliver in time leaves D untouched for the elements concerned, sets the device status word
