@@ -12,6 +12,13 @@ thread_local std::string g_last_error;
 }
 
 void set_last_error(const char* text) { g_last_error = text ? text : ""; }
+void set_last_error_at(const char* text, const char* call) {
+    g_last_error = text ? text : "";
+    if (call != nullptr) {
+        g_last_error += ": ";
+        g_last_error.append(call, std::strlen(call) < 160 ? std::strlen(call) : 160);
+    }
+}
 
 int default_use_pdl() {
     static const int value = [] {

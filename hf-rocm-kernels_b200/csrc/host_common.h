@@ -11,6 +11,7 @@
 namespace hfrk {
 
 void set_last_error(const char* text);
+void set_last_error_at(const char* text, const char* call);
 
 // 1 unless the environment switches programmatic dependent launch off for the plain entry points
 // (HFRK_PDL=0). With it the weight stream of a call starts while the previous kernel on the stream
@@ -20,12 +21,13 @@ int default_use_pdl();
 
 }  // namespace hfrk
 
-#define HFRK_CUDA_TRY(expr)                                      \
-    do {                                                         \
-        cudaError_t hfrk_err_ = (expr);                          \
-        if (hfrk_err_ != cudaSuccess) {                          \
-            ::hfrk::set_last_error(cudaGetErrorString(hfrk_err_)); \
-            (void)cudaGetLastError();                            \
-            return HFRK_CUDA_ERROR;                              \
-        }                                                        \
+// On failure hfrk_last_error() reads "<CUDA's message>: <the call that failed>".
+#define HFRK_CUDA_TRY(expr)                                                    \
+    do {                                                                       \
+        cudaError_t hfrk_err_ = (expr);                                        \
+        if (hfrk_err_ != cudaSuccess) {                                        \
+            ::hfrk::set_last_error_at(cudaGetErrorString(hfrk_err_), #expr);   \
+            (void)cudaGetLastError();                                          \
+            return HFRK_CUDA_ERROR;                                            \
+        }                                                                      \
     } while (0)

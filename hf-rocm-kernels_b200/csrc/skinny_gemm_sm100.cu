@@ -1241,7 +1241,21 @@ extern "C" int hfrk_skinny_gemm_fp8_host_batch(const hfrk_host_call* calls, int 
                 run += bytes;
                 ++j;
             }
-            HFRK_CUDA_TRY(cudaMemcpyAsync(base + dev_off, host0, run, cudaMemcpyHostToDevice, res->copy_stream));
+            cudaError_t merged = cudaMemcpyAsync(base + dev_off, host0, run, cudaMemcpyHostToDevice, res->copy_stream);
+            if (merged != cudaSuccess && j > i + 1) {
+                // blocks that follow each other in the address space but come from different page-locked
+                // allocations cannot travel as one copy (refused at submission): one copy per block then
+                (void)cudaGetLastError();
+                size_t done = 0;
+                for (int t = i; t < j; ++t) {
+                    const size_t bytes = static_cast<size_t>(calls[t].m) * calls[t].k;
+                    HFRK_CUDA_TRY(cudaMemcpyAsync(base + dev_off + done, calls[t].A_host, bytes, cudaMemcpyHostToDevice,
+                                                  res->copy_stream));
+                    done += bytes;
+                }
+            } else {
+                HFRK_CUDA_TRY(merged);
+            }
             // D_in of the chunk's accumulating calls travels with it, so that nothing but kernels sits
             // on the compute stream (a copy between two kernels would end their overlap)
             for (int t = i; t < j; ++t) {
@@ -1249,7 +1263,7 @@ extern "C" int hfrk_skinny_gemm_fp8_host_batch(const hfrk_host_call* calls, int 
                 size_t off = 0;
                 for (int u = 0; u < t; ++u)
                     off += align16(static_cast<size_t>(calls[u].m) * calls[u].n * out_elem_bytes(calls[u].d_dtype));
-                HFRK_CUDA_TRY(cudaMemcpyAsync(d_base + off, calls[t].D_host,
+                HFRK_CUDA_TRY(cudaMemcpyAsync(d_base + off, calls[t].D_in_host != nullptr ? calls[t].D_in_host : calls[t].D_host,
                                               static_cast<size_t>(calls[t].m) * calls[t].n * out_elem_bytes(calls[t].d_dtype),
                                               cudaMemcpyHostToDevice, res->copy_stream));
             }
@@ -1289,7 +1303,19 @@ extern "C" int hfrk_skinny_gemm_fp8_host_batch(const hfrk_host_call* calls, int 
                 dev_run += align16(bytes);
                 ++j;
             }
-            HFRK_CUDA_TRY(cudaMemcpyAsync(host0, d_base + off, run, cudaMemcpyDeviceToHost, res->copy_stream));
+            cudaError_t merged = cudaMemcpyAsync(host0, d_base + off, run, cudaMemcpyDeviceToHost, res->copy_stream);
+            if (merged != cudaSuccess && j > i + 1) {
+                (void)cudaGetLastError();   // neighbours from different page-locked allocations, as above
+                size_t done = 0;
+                for (int t = i; t < j; ++t) {
+                    const size_t bytes = static_cast<size_t>(calls[t].m) * calls[t].n * out_elem_bytes(calls[t].d_dtype);
+                    HFRK_CUDA_TRY(cudaMemcpyAsync(calls[t].D_host, d_base + off + done, bytes, cudaMemcpyDeviceToHost,
+                                                  res->copy_stream));
+                    done += bytes;
+                }
+            } else {
+                HFRK_CUDA_TRY(merged);
+            }
             // device blocks are padded to 16 bytes: a run only continues while no padding intervened
             for (int t = i; t < j; ++t)
                 off += align16(static_cast<size_t>(calls[t].m) * calls[t].n * out_elem_bytes(calls[t].d_dtype));

@@ -113,7 +113,7 @@ class HostCall(ctypes.Structure):
     _fields_ = [("A_host", ctypes.c_void_p), ("W_dev", ctypes.c_void_p), ("D_host", ctypes.c_void_p),
                 ("scale_dev", ctypes.c_void_p), ("m", ctypes.c_int), ("n", ctypes.c_int), ("k", ctypes.c_int),
                 ("w_row_stride", ctypes.c_int64), ("a_kind", ctypes.c_int), ("w_kind", ctypes.c_int),
-                ("d_dtype", ctypes.c_int), ("accumulate", ctypes.c_int)]
+                ("d_dtype", ctypes.c_int), ("accumulate", ctypes.c_int), ("D_in_host", ctypes.c_void_p)]
 
 
 lib = _load()
@@ -242,14 +242,18 @@ def skinny_gemm_host(a_host, w_dev, d_host, scale_dev, work_dev, accumulate=True
 
 class HostBatch:
     """A fixed list of host-buffer GEMM calls, prepared once and queued with one library call per
-    step (``hfrk_skinny_gemm_fp8_host_batch``). ``calls`` = [(a_host, w_dev, d_host, scale_dev, accumulate)];
-    the tensors must outlive the object, the host ones should be page-locked."""
+    step (``hfrk_skinny_gemm_fp8_host_batch``). ``calls`` = [(a_host, w_dev, d_host, scale_dev, accumulate)] or
+    [(a_host, w_dev, d_host, scale_dev, accumulate, d_in_host)]: with ``d_in_host`` (a read-only, bias-filled
+    host tensor) D_in is read from there and ``d_host`` only receives the result. The tensors must outlive
+    the object, the host ones should be page-locked."""
 
     def __init__(self, calls, device: torch.device):
         self.device = device
         self.array = (HostCall * len(calls))()
         self.keep = list(calls)
-        for slot, (a_host, w_dev, d_host, scale_dev, accumulate) in zip(self.array, calls):
+        for slot, call in zip(self.array, calls):
+            a_host, w_dev, d_host, scale_dev, accumulate = call[:5]
+            d_in_host = call[5] if len(call) > 5 else None
             m, k = a_host.shape
             n = w_dev.shape[0]
             assert a_host.device.type == "cpu" and d_host.device.type == "cpu" and w_dev.stride(1) == 1
@@ -258,6 +262,10 @@ class HostBatch:
             slot.scale_dev, slot.m, slot.n, slot.k = scale_dev.data_ptr(), m, n, k
             slot.w_row_stride, slot.a_kind, slot.w_kind = w_dev.stride(0), fp8_kind(a_host.dtype), fp8_kind(w_dev.dtype)
             slot.d_dtype, slot.accumulate = out_kind(d_host.dtype), int(accumulate)
+            if d_in_host is not None:
+                assert d_in_host.device.type == "cpu" and d_in_host.is_contiguous() and d_in_host.shape == d_host.shape
+                assert d_in_host.dtype == d_host.dtype
+                slot.D_in_host = d_in_host.data_ptr()
         self.work_bytes = lib.hfrk_host_batch_workspace_bytes(self.array, len(calls))
         assert self.work_bytes > 0, "invalid call in the batch"
         self.work = torch.empty(self.work_bytes, dtype=torch.uint8, device=device)

@@ -149,6 +149,9 @@ typedef struct hfrk_host_call {
     int m, n, k;
     int64_t w_row_stride;
     int a_kind, w_kind, d_dtype, accumulate;
+    const void* D_in_host;   /* accumulate != 0: where D_in is read from; NULL = from D_host itself. A
+                              * separate, read-only bias-filled buffer spares the caller the refill of
+                              * D_host before every step. */
 } hfrk_host_call;
 int64_t hfrk_host_batch_workspace_bytes(const hfrk_host_call* calls, int count);
 int hfrk_skinny_gemm_fp8_host_batch(const hfrk_host_call* calls, int count, void* work_dev,

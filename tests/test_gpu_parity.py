@@ -345,17 +345,22 @@ def test_host_batch_equals_the_device_calls(capi, dev, pinned, packed):
         d_host.copy_(d0)
         want = d0.to(dev).clone()
         capi.check(capi.skinny_gemm(a.view(torch.float8_e4m3fn).to(dev), w, want, scale, accumulate=bias))
-        calls.append((a_host.view(torch.float8_e4m3fn), w, d_host, scale, bias))
+        # every other accumulating call reads D_in from a separate read-only buffer instead of d_host
+        d_in_host = d0.clone().pin_memory() if (bias and pinned and len(calls) % 2 == 0) else None
+        calls.append((a_host.view(torch.float8_e4m3fn), w, d_host, scale, bias, d_in_host))
         expect.append((want, d0))
     torch.cuda.synchronize()
     batch = capi.HostBatch(calls, dev)
     stream = torch.cuda.Stream()
     for _ in range(2):
-        for (a_host, w, d_host, scale, bias), (want, d0) in zip(calls, expect):
-            d_host.copy_(d0)
+        for (a_host, w, d_host, scale, bias, d_in_host), (want, d0) in zip(calls, expect):
+            if d_in_host is None:
+                d_host.copy_(d0)
+            else:
+                d_host.fill_(7.0)              # must not be read
         capi.check(batch.queue(stream))
         stream.synchronize()
-        for (a_host, w, d_host, scale, bias), (want, d0) in zip(calls, expect):
+        for (a_host, w, d_host, scale, bias, d_in_host), (want, d0) in zip(calls, expect):
             assert torch.equal(d_host, want.cpu())
     assert capi.device_status(clear=True)[0] == 0
     # too little scratch and an invalid entry are refused
