@@ -360,8 +360,20 @@ struct EpiCtx {
     float scale;
 };
 
+// Receive buffer of an owner of token rows: float [sender][group][128 threads][rows per group] with
+// rows per group = min(rpo, 4) = what one asynchronous store carries. The 128 threads' pieces of a
+// group lie side by side, so the stores of a warp cover one contiguous run of the owner's shared
+// memory; with the pieces of one thread side by side instead (a stride of 32 or 64 bytes between
+// lanes once rpo reaches 8) every 16 token rows cost 1.3 us instead of 0.26 us.
+__device__ __forceinline__ uint32_t recv_float_index(int sender, int tid, int row_in_owner, int rows_log2) {
+    const int g_log2 = rows_log2 < 2 ? rows_log2 : 2;
+    const int groups_log2 = rows_log2 - g_log2;
+    return static_cast<uint32_t>(((((sender << groups_log2) + (row_in_owner >> g_log2)) * kTileN + tid) << g_log2) +
+                                 (row_in_owner & ((1 << g_log2) - 1)));
+}
+
 // Sends 16 token rows (c0 .. c0 + 15) of this thread's W row to the CTAs that finish them. Token
-// row r goes to CTA r >> rows_log2, position r & (rpo - 1) of this thread's slot there. Rows leave
+// row r goes to CTA r >> rows_log2, row r & (rpo - 1) of this sender's block there. Rows leave
 // 1, 2 or 4 at a time (min(rpo, 4)); a group never straddles two owners because its size divides
 // rpo. An owner expects whole blocks, so the rows of its range past m are sent as they are.
 __device__ __forceinline__ void send_partial_rows(const GemmParams& p, const EpiCtx& cx, int c0, const uint32_t (&v)[16]) {
@@ -373,8 +385,8 @@ __device__ __forceinline__ void send_partial_rows(const GemmParams& p, const Epi
             const int r0 = c0 + g;
             const uint32_t q = static_cast<uint32_t>(r0 >> p.rows_log2);
             if (static_cast<int>(q << p.rows_log2) < p.m) {
-                st_async_v4_b32(dsmem_map(send_base + 4u * (r0 & (rpo - 1)), q), v[g], v[g + 1], v[g + 2], v[g + 3],
-                                dsmem_map(cx.recv_bar, q));
+                const uint32_t at = cx.recv_addr + 4u * recv_float_index(cx.rank, threadIdx.x, r0 & (rpo - 1), p.rows_log2);
+                st_async_v4_b32(dsmem_map(at, q), v[g], v[g + 1], v[g + 2], v[g + 3], dsmem_map(cx.recv_bar, q));
             }
         }
     } else if (rpo == 2) {
@@ -545,8 +557,8 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
     bool landed = ok && (!owner || mbar_wait_bounded(cx.recv_bar, 0u, &cx.ctrl->abort, kRoleEpilogue));
     landed = __all_sync(0xffffffffu, landed);
     if (!landed || !owner) return;
-    const float* const mine = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(cx.ctrl) + kCtrlBytes) +
-                              (static_cast<size_t>(tid) << p.rows_log2);   // [sender] at a stride of 128 * rpo
+    const float* const recv = reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(cx.ctrl) + kCtrlBytes);
+    const float* const mine = recv + recv_float_index(0, tid, 0, p.rows_log2);   // [sender] at a stride of 128 * rpo
     const int sender_stride = kTileN << p.rows_log2;
     float own[kOwned];
 #pragma unroll
@@ -567,7 +579,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
             const float4 f = *reinterpret_cast<const float4*>(mine + q * sender_stride);
             own[0] += f.x; own[1] += f.y; own[2] += f.z; own[3] += f.w;
             if (rpo >= 8) {
-                const float4 g = *reinterpret_cast<const float4*>(mine + q * sender_stride + 4);
+                const float4 g = *reinterpret_cast<const float4*>(mine + q * sender_stride + 4 * kTileN);   // second group
                 own[4] += g.x; own[5] += g.y; own[6] += g.z; own[7] += g.w;
             }
         }
@@ -591,15 +603,24 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
             idx += p.n;
         }
     }
-    // more than 16 tokens with a small split: an owner finishes more than kOwned rows
-    for (int it = kOwned; it < rpo; ++it) {
-        const int row = own_row0 + it;
-        if (row >= p.m) break;
-        float sum = 0.0f;
-        for (int q = 0; q < p.split; ++q) sum += mine[q * sender_stride + it];
-        const size_t idx = static_cast<size_t>(row) * p.n + n;
-        const float d0 = p.accumulate ? load1<DT>(p.d, idx) : 0.0f;
-        store1<DT>(p.d, idx, fmaf(sum, cx.scale, d0));
+    // more than 16 tokens with a small split: an owner finishes more than kOwned rows, four at a time
+    for (int g = kOwned / 4; g < (rpo >> 2); ++g) {
+        const int row0 = own_row0 + 4 * g;
+        if (row0 >= p.m) break;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int q = 0; q < p.split; ++q) {
+            const float4 f = *reinterpret_cast<const float4*>(mine + q * sender_stride + g * 4 * kTileN);
+            sum.x += f.x; sum.y += f.y; sum.z += f.z; sum.w += f.w;
+        }
+        const float part[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (row0 + j < p.m) {
+                const size_t idx = static_cast<size_t>(row0 + j) * p.n + n;
+                const float d0 = p.accumulate ? load1<DT>(p.d, idx) : 0.0f;
+                store1<DT>(p.d, idx, fmaf(part[j], cx.scale, d0));
+            }
+        }
     }
 }
 
@@ -691,7 +712,7 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const EpiCt
         for (int it = 0; it < kOwned; ++it) {
             float sum = 0.0f;
             if (it < rows) {
-                for (int q = 0; q < p.split; ++q) sum += recv[((q * kTileN + tid) << p.rows_log2) + it];
+                for (int q = 0; q < p.split; ++q) sum += recv[recv_float_index(q, tid, it, p.rows_log2)];
         }
             y[it] = round_trip_16(sum * cx.scale, p.d_dtype);
         }
