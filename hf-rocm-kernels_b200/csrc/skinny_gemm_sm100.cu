@@ -279,16 +279,33 @@ int make_plan(const DeviceModel& dm, int m, int n, int k, int split_req, int sta
         split = 1;
         if (tiles < dm.sms) {
             // largest resident split; a ring of three stages lets three CTAs share an SM, four stages
-            // two. More CTAs win; with equal CTAs the longer ring does.
+            // two. Up to 16 tokens more CTAs win; with equal CTAs the longer ring does.
+            // Above 16 tokens the activation tile and the receive buffer grow and the choices thin
+            // out: a ring of two stages may be all that lets three CTAs share an SM. There the bytes
+            // in flight decide (CTAs x stages), marked down by a quarter when an owner finishes more
+            // than eight token rows (the reduction then runs past its register path); equal scores
+            // go to more CTAs. 8192 x 8192, 48 tokens: 15.4 us with 64 clusters of 6 on two stages,
+            // 18.2 us with clusters of 4 on three; 6144 x 4096, 32 tokens: 7.7 us with clusters of 5
+            // on four stages, 8.9 us with clusters of 7 on two.
             int best_ctas = 0;
-            const int ring_choices[2] = {3, 4};
-            for (int choice = 0; choice < 2; ++choice) {
+            long best_score = 0;
+            const int ring_choices[3] = {2, 3, 4};
+            for (int choice = m_pad > 16 ? 0 : 1; choice < 3; ++choice) {
                 const int ring = stages_req != 0 ? stages_req : ring_choices[choice];
                 for (int s = kMaxSplit; s >= 2; --s) {
                     if (nkb / s < 2) continue;
                     if (!resident(s, ring)) continue;
-                    if (tiles * s >= best_ctas) {
-                        best_ctas = tiles * s;
+                    const int ctas = tiles * s;
+                    bool better;
+                    if (m_pad > 16) {
+                        const long score = static_cast<long>(ctas) * ring * (rows_per_owner_log2(m, s) > 3 ? 3 : 4);
+                        better = score > best_score || (score == best_score && ctas > best_ctas);
+                        if (better) best_score = score;
+                    } else {
+                        better = ctas >= best_ctas;
+                    }
+                    if (better) {
+                        best_ctas = ctas;
                         split = s;
                         if (stages_req == 0) stages = ring;
                     }
