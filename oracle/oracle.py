@@ -206,15 +206,20 @@ def accumulation_floor(a_q: np.ndarray, w_q: np.ndarray, scale: float, a_kind: i
 # How many elements of one case may exceed the stated bound itself while staying inside bound + floor.
 # Observed over every parity case (126 cases, 0 to 459k outputs each): none in any case of up to 262,144
 # outputs at K <= 5120; 1 of 458,752 outputs at K = 4096 (ratio 1.6); 3 of 229,376 at K = 8192 (ratio
-# 1.4); at most 4 per case at K >= 14336 (outputs that cancel to within ~1e-6 of zero). The cap is an
-# absolute count, not a share of the outputs.
+# 1.4), 6 of 917,504 at K = 8192 (ratio 2.2); at most 4 per case at K >= 14336 (outputs that cancel to
+# within ~1e-6 of zero). The cap is a count per 262,144 outputs (3e-5 of them), not a loose share.
 MAX_STRICT_EXCEPTIONS = 8
 
 
 def strict_exception_cap(k: int, count: int = 0) -> int:
     """Elements of a case of ``count`` outputs that may lie beyond :func:`tolerance` (never beyond
-    tolerance + floor): none for short reductions and moderate output counts, a handful otherwise."""
-    return 0 if (k <= 5120 and count <= 262144) else MAX_STRICT_EXCEPTIONS
+    tolerance + floor): none for short reductions and moderate output counts, otherwise a handful
+    per 262,144 outputs (the largest case, 917,504 outputs at K = 8192, showed 6: which elements
+    nearly cancel depends on the summation order, that is on the K split the planner picks for the
+    chip, so the cap leaves room beside what one chip showed)."""
+    if k <= 5120 and count <= 262144:
+        return 0
+    return MAX_STRICT_EXCEPTIONS * max(1, -(-count // 262144))
 
 
 def compare(out32: np.ndarray, ref32: np.ndarray, k: int, scale: float, d_dtype: int = BF16,

@@ -7,7 +7,7 @@ For outputs that land within ~1e-3 of zero this bound drops below what ANY fp32 
 signed products can guarantee (tests/test_oracle_golden.py shows a host float32 matmul breaking it
 in two summation orders), so such elements are allowed the accumulation floor of
 ``oracle.accumulation_floor`` on top; their number is capped at ``oracle.strict_exception_cap(K)``:
-none for K <= 5120 and up to 262,144 outputs, at most 8 per case otherwise. With HFRK_PARITY_SUMMARY=<path> in the environment
+none for K <= 5120 and up to 262,144 outputs, at most 8 per 262,144 outputs otherwise. With HFRK_PARITY_SUMMARY=<path> in the environment
 the per-case counts are written to that file as JSON lines.
 """
 import math

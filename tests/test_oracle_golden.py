@@ -160,4 +160,4 @@ def test_float32_accumulation_cannot_hold_the_stated_bound_on_cancelling_outputs
         assert res["max_err_over_tol"] > 3.0, res
         assert res["hard_violations"] == 0, res                 # bound + floor holds
     assert o.strict_exception_cap(5120, 262144) == 0 and o.strict_exception_cap(8192, 16) == o.MAX_STRICT_EXCEPTIONS == 8
-    assert o.strict_exception_cap(4096, 458752) == 8
+    assert o.strict_exception_cap(4096, 458752) == 16 and o.strict_exception_cap(8192, 917504) == 32
