@@ -351,7 +351,7 @@ __device__ __forceinline__ void store16(void* d, size_t idx, const float (&y)[16
 struct EpiCtx {
     Ctrl* ctrl;
     uint8_t* ring_ptr;      // start of the (by then idle) stage ring
-    uint32_t recv_addr;     // shared-memory address of float recv[split][128][rpo]
+    uint32_t recv_addr;     // shared-memory address of the receive buffer (recv_float_index)
     uint32_t recv_bar;
     uint32_t accum_bar;
     uint32_t lane_taddr;    // TMEM address of this thread's lane, column 0

@@ -148,7 +148,7 @@ int rows_per_owner_log2(int m, int split) {
     return lg;
 }
 
-// Receive buffer of the split-K reduction: float [split][128][rows per owner].
+// Receive buffer of the split-K reduction: split x 128 x rows-per-owner floats (layout: recv_float_index).
 int recv_buffer_bytes(int m, int split) {
     return split > 1 ? split * kTileN * 4 * (1 << rows_per_owner_log2(m, split)) : 0;
 }
