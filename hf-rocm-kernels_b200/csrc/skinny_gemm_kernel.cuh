@@ -99,7 +99,8 @@ __device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* ptr) {
 }
 
 // All-reduce of the values this thread owns, fused into the GEMM epilogue. `val` holds CNT partial
-// sums, `slot[i]` the element's index in the exchange buffer (0xffffffff = unused). All ranks run
+// sums of which the first `valid` are in use; element i sits at index slot0 + i * 128 of the exchange
+// buffer (consecutive token rows of one output column: no per-element index is kept in registers). All ranks run
 // the same launch shape, so "this thread's element i" names the same output element on every rank.
 //
 // One-shot (rp.two_shot == 0): the thread writes {value, epoch} cells into every peer's buffer
@@ -115,7 +116,7 @@ __device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* ptr) {
 // Either way all ranks end with bit-identical sums. Nothing here synchronises the CTA; every wait
 // is bounded. Returns false if a peer did not deliver in time (the status word is set).
 template <int CNT, int WORLD>
-__device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
+__device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsigned int epoch, uint32_t slot0, int valid,
                                                 float (&val)[CNT], volatile uint32_t* abort_flag) {
     // WORLD > 0: the group size is known at compile time, so the loops over the ranks unroll to exactly
     // that many cells; WORLD == 0 is the general form (any size up to kMaxWorld).
@@ -131,22 +132,19 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
         uint2* dst = rp.cells[peer] + my_src * rp.elems_per_src;
 #pragma unroll
         for (int i = 0; i < CNT; ++i) {
-            if (slot[i] != 0xffffffffu) st_relaxed_sys_v2(dst + slot[i], __float_as_uint(val[i]), epoch);
+            if (i < valid) st_relaxed_sys_v2(dst + slot0 + i * kTileN, __float_as_uint(val[i]), epoch);
         }
     }
-    // Cells are fetched a batch at a time (4 elements x up to 7 peers in flight per thread) and the
+    // Cells are fetched a batch at a time (4 elements x up to 3 peers, or 2 x 7, in flight per thread) and the
     // batch is re-read until every cell shows the epoch; batches of unused elements are skipped,
     // which is the common case: a thread usually owns two or three elements of the tile.
-    constexpr int kBatch = 4;
+    constexpr int kBatch = kSrcs > 4 ? 2 : 4;   // cells in flight per thread: kBatch x (ranks - 1)
     bool ok = true;
     const long long start = clock64();
     const uint2* const mine = rp.cells[rp.rank] + parity * sources * rp.elems_per_src;
 #pragma unroll
     for (int i0 = 0; i0 < CNT; i0 += kBatch) {
-        bool any = false;
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) any |= slot[i0 + b] != 0xffffffffu;
-        if (!any || !ok) continue;
+        if (i0 >= valid || !ok) continue;
         if (gather) {
             uint32_t got[kBatch][kSrcs];
             for (;;) {
@@ -156,9 +154,9 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
 #pragma unroll
                     for (int src = 0; src < kSrcs; ++src) {
                         got[b][src] = 0u;
-                        if (src < world && src != rp.rank && slot[i0 + b] != 0xffffffffu) {
+                        if (src < world && src != rp.rank && i0 + b < valid) {
                             const uint2 cell =
-                                ld_relaxed_sys_v2(mine + static_cast<size_t>(src) * rp.elems_per_src + slot[i0 + b]);
+                                ld_relaxed_sys_v2(mine + static_cast<size_t>(src) * rp.elems_per_src + slot0 + (i0 + b) * kTileN);
                             got[b][src] = cell.x;
                             ready &= cell.y == epoch;
                         }
@@ -189,8 +187,8 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
                     if (peer == rp.rank) continue;
 #pragma unroll
                     for (int b = 0; b < kBatch; ++b) {
-                        if (slot[i0 + b] != 0xffffffffu)
-                            st_relaxed_sys_v2(rp.cells[peer] + fin + slot[i0 + b], __float_as_uint(val[i0 + b]), epoch);
+                        if (i0 + b < valid)
+                            st_relaxed_sys_v2(rp.cells[peer] + fin + slot0 + (i0 + b) * kTileN, __float_as_uint(val[i0 + b]), epoch);
                     }
                 }
             }
@@ -203,8 +201,8 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
 #pragma unroll
                 for (int b = 0; b < kBatch; ++b) {
                     got[b] = 0u;
-                    if (slot[i0 + b] != 0xffffffffu) {
-                        const uint2 cell = ld_relaxed_sys_v2(fin + slot[i0 + b]);
+                    if (i0 + b < valid) {
+                        const uint2 cell = ld_relaxed_sys_v2(fin + slot0 + (i0 + b) * kTileN);
                         got[b] = cell.x;
                         ready &= cell.y == epoch;
                     }
@@ -220,7 +218,7 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
             if (!ok) continue;
 #pragma unroll
             for (int b = 0; b < kBatch; ++b) {
-                if (slot[i0 + b] != 0xffffffffu) val[i0 + b] = __uint_as_float(got[b]);
+                if (i0 + b < valid) val[i0 + b] = __uint_as_float(got[b]);
             }
         }
     }
@@ -232,9 +230,9 @@ __device__ __forceinline__ bool rowpar_exchange_impl(const RowparDev& rp, unsign
 // ranks, most of them predicated off, cost microseconds of issue time per call. kWorld = 0 is the
 // general form.
 template <int CNT, int kWorld>
-__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, const uint32_t (&slot)[CNT],
+__device__ __forceinline__ bool rowpar_exchange(const RowparDev& rp, unsigned int epoch, uint32_t slot0, int valid,
                                                 float (&val)[CNT], volatile uint32_t* abort_flag) {
-    return rowpar_exchange_impl<CNT, kWorld>(rp, epoch, slot, val, abort_flag);
+    return rowpar_exchange_impl<CNT, kWorld>(rp, epoch, slot0, valid, val, abort_flag);
 }
 
 // Instantiations of the kernel.
@@ -493,13 +491,11 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
             if (kRowPar) {
                 // host guarantees m <= 16 here: one load, 16 values per thread
                 float val[16];
-                uint32_t slot[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    val[j] = __uint_as_float(v[j]);
-                    slot[j] = j < p.m ? tile_slot0 + static_cast<uint32_t>(j * kTileN + tid) : 0xffffffffu;
-                }
-                if (!rowpar_exchange<16, kWorld>(p.rp, epoch, slot, val, &cx.ctrl->abort)) ok = false;
+                for (int j = 0; j < 16; ++j) val[j] = __uint_as_float(v[j]);
+                if (!rowpar_exchange<16, kWorld>(p.rp, epoch, tile_slot0 + static_cast<uint32_t>(tid), min(p.m, 16), val,
+                                                 &cx.ctrl->abort))
+                    ok = false;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(val[j]);
             }
@@ -585,13 +581,10 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const EpiCtx
         }
     }
     if (kRowPar) {
-        uint32_t slot[kOwned];
-#pragma unroll
-        for (int it = 0; it < kOwned; ++it) {
-            const int row = own_row0 + it;
-            slot[it] = (it < rpo && row < p.m) ? tile_slot0 + static_cast<uint32_t>(row * kTileN + tid) : 0xffffffffu;
-        }
-        if (!rowpar_exchange<kOwned, kWorld>(p.rp, epoch, slot, own, &cx.ctrl->abort)) return;
+        const int valid = max(0, min(min(rpo, kOwned), p.m - own_row0));
+        if (!rowpar_exchange<kOwned, kWorld>(p.rp, epoch, tile_slot0 + static_cast<uint32_t>(own_row0 * kTileN + tid), valid,
+                                             own, &cx.ctrl->abort))
+            return;
     }
     if (!lane_valid) return;
     {
@@ -766,9 +759,11 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const EpiCt
 // kDT / kWorld: the plain and the gate/up kernel decide the output type at run time (kDT = -1); the
 // row-parallel kernel is instantiated per output type and group size (2, 4, 8, or 0 = any), because
 // one kernel holding every exchange variant needed 168 registers with spills and cost 2-3 us per
-// call more than the plain kernel even in a group of one.
+// call more than the plain kernel even in a group of one. It is compiled for three CTAs per SM
+// (at most 112 registers; a few tens of bytes spill in the exchange) so that it runs the launch
+// shapes the planner picks for the plain kernel.
 template <int kMode, int kDT = -1, int kWorld = 0>
-__global__ void __launch_bounds__(kThreads, HFRK_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, kMode == kModeRowPar ? 3 : HFRK_MIN_CTAS)
 skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];

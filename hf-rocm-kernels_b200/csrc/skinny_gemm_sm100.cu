@@ -616,8 +616,7 @@ int launch_gemm(const void* A, const void* W, void* D, const float* scale_dev, i
         // the exchange buffer of the row-parallel kernel is laid out in 128-row tiles
         rc = make_plan(device_model(stream), mc, n, k, split_req, stages_req, &plan,
                        rowpar != nullptr ? kAutoTileRowsOff : tile_rows_req,
-                       // the row-parallel instantiation keeps the exchange in registers: two CTAs per SM
-                       rowpar != nullptr ? 2 : kModelMaxPerSm);
+                       kModelMaxPerSm);   // the row-parallel instantiations are compiled for three CTAs per SM too
         if (rc != HFRK_SUCCESS) return rc;
         CUtensorMap tmap_w;
         rc = get_tensor_map(W, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
