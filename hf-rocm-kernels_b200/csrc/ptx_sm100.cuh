@@ -193,6 +193,11 @@ __device__ __forceinline__ void cluster_arrive_release() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
 
+// Arrival without memory ordering: for threads that have written nothing the peers will read.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void cluster_wait_acquire() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }

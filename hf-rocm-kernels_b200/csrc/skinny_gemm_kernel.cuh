@@ -863,8 +863,17 @@ skinny_gemm_fp8_sm100_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
     pdl_launch_dependents();
     // Every CTA of the cluster has initialised its barriers once this cluster barrier completes;
-    // it is only waited for much later, right before partials are pushed to the peers.
-    if (p.split > 1) cluster_arrive_release();
+    // it is only waited for much later, right before partials are pushed to the peers. Only the
+    // producer warp, which initialised them, arrives with release semantics: the release costs the
+    // arriving thread ~1.8 us (measured from CTA entry to the end of set-up with and without a
+    // cluster), and the MMA thread would spend it in front of its first K block.
+    if (p.split > 1) {
+        if (warp == kProducerWarp) {
+            cluster_arrive_release();
+        } else {
+            cluster_arrive_relaxed();
+        }
+    }
     const uint32_t tmem_acc = ctrl->tmem_base;
     if (threadIdx.x == 0) stamp(p, 1);
 
