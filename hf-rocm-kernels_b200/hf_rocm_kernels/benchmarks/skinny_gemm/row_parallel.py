@@ -2,9 +2,10 @@
 followed by an NCCL all-reduce, and against the local GEMM alone.
 
     torchrun --nnodes=1 --nproc-per-node 4 --master-addr 127.0.0.1 --master-port 29555 \\
-        -m hf_rocm_kernels.benchmarks.skinny_gemm.row_parallel --tokens 1 16 --n 8192 --k 28672
+        -m hf_rocm_kernels.benchmarks.skinny_gemm.row_parallel --tokens 1 16 -n 8192 -k 28672
     python -m hf_rocm_kernels.benchmarks.skinny_gemm.row_parallel --tokens 16 --plain-calls 3      # one GPU, for a profiler
 
+(Under torchrun give the sizes as -n / -k: its own parser takes --n for an abbreviation of its options.)
 Each rank holds K / world columns. Times are microseconds per call from a CUDA graph of 16 calls on 16
 different weight shards, the maximum over ranks. Without torchrun the script runs as a group of one.
 """
@@ -49,8 +50,8 @@ def _graph_time_us(calls, device, world: int, reps: int = 20, warm: int = 5) -> 
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--tokens", nargs="+", type=int, default=[1, 16])
-    parser.add_argument("--n", type=int, default=8192)
-    parser.add_argument("--k", type=int, default=28672, help="the whole K; every rank takes K / world of it")
+    parser.add_argument("-n", "--n", type=int, default=8192)
+    parser.add_argument("-k", "--k", type=int, default=28672, help="the whole K; every rank takes K / world of it")
     parser.add_argument("--plain-calls", type=int, default=0,
                         help="only issue this many plain (non-graph) fused calls per token count and exit")
     args = parser.parse_args()

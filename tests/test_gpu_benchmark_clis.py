@@ -21,7 +21,7 @@ COMMANDS = [
      ["--m", "4", "--n", "1024", "--k", "1024", "--split-k", "2", "--stages", "3", "--iterations", "4"], "us"),
     ("hf_rocm_kernels.benchmarks.skinny_gemm.row_parallel", ["--tokens", "4", "--n", "1024", "--k", "2048"],
      "fused one-shot"),
-    ("hf_rocm_kernels.benchmarks.skinny_gemm.row_parallel", ["--tokens", "4", "--n", "1024", "--k", "2048",
+    ("hf_rocm_kernels.benchmarks.skinny_gemm.row_parallel", ["--tokens", "4", "-n", "1024", "-k", "2048",   # as under torchrun
                                                              "--plain-calls", "2"], "fused calls of m=4"),
     ("hf_rocm_kernels.benchmarks.swiglu.vs_reference", ["-r", "1", "16", "-i", "1024", "-b", "256"], "Vectorized"),
     ("hf_rocm_kernels.benchmarks.residual_rms.vs_reference", ["-r", "1", "16", "-c", "1024", "-b", "256"], "Vectorized"),
