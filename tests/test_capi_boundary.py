@@ -121,6 +121,26 @@ def test_plan_follows_the_device_model(capi):
         assert capi.plan(16, 4096, 4096)["ctas"] <= 3 * 74
     finally:
         capi.override_device_model(capacity=None)
+    # More than 16 tokens, with the capacities measured on one B200: candidates (largest resident split of a
+    # ring of 2, 3 and 4 stages) are ranked by bytes in flight, marked down when an owner finishes more than 8
+    # token rows; equal scores go to more CTAs.
+    measured = _fake_capacity(148, gpcs)
+    for split, caps in {8: (15, 33, 48), 7: (15, 37, 56), 6: (22, 45, 71), 5: (26, 56, 82), 4: (33, 71, 104)}.items():
+        measured[split] = [0] + list(caps)
+    for split in range(9, 17):
+        measured[split] = [0, 7, 14, 21]
+    capi.override_device_model(148, measured)
+    try:
+        picks = {(48, 8192, 8192): (6, 2), (32, 8192, 8192): (4, 4), (32, 6144, 4096): (5, 4), (48, 6144, 4096): (7, 2),
+                 (24, 10240, 8192): (3, 4), (32, 10240, 8192): (5, 2), (64, 4096, 4096): (8, 3), (64, 6144, 4096): (4, 3)}
+        for (m, n, k), (split, stages) in picks.items():
+            p = capi.plan(m, n, k)
+            assert (p["split_k"], p["num_stages"]) == (split, stages), ((m, n, k), p)
+        # up to 16 tokens the rule is unchanged: more CTAs win, the table pins the Llama-3 shapes
+        assert (capi.plan(16, 4096, 4096)["split_k"], capi.plan(16, 4096, 4096)["num_stages"]) == (7, 5)
+        assert (capi.plan(16, 6144, 4096)["split_k"], capi.plan(16, 6144, 4096)["num_stages"]) == (7, 3)
+    finally:
+        capi.override_device_model(capacity=None)
     model = capi.device_model()
     assert model["sms"] >= 1 and len(model["capacity"]) == 17
     try:
