@@ -263,6 +263,23 @@ def test_token_counts_above_one_launch(capi, dev, checker, m):
     checker(_run_c(capi, a, w, s, d_in, case.m, case.n, variant=2), a, w, scale, d_in, f"m{m}_streamk")
 
 
+@pytest.mark.parametrize("m,split,stages", [(17, 16, 2), (24, 6, 2), (33, 2, 3), (40, 5, 2), (48, 6, 2), (48, 4, 3),
+                                            (64, 8, 3), (64, 3, 2), (50, 7, 2)])
+def test_split_k_above_16_tokens(capi, dev, checker, m, split, stages):
+    """The in-cluster reduction with 2 to 32 token rows per owner (one to eight groups of four rows in the
+    receive buffer, owners whose range reaches past m, owners with nothing to finish), fp16 and bf16."""
+    from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
+
+    case = wl.Case(8, 300 + m + split, "bigm_split", m, 2000, 4096, bias=(m % 2 == 0))
+    dtype = torch.float16 if split % 2 else torch.bfloat16
+    a, w, s, d_in, scale = _case_on_device(case, dev, out_dtype=dtype)
+    assert capi.plan(m, case.n, case.k, split_k=split)["split_k"] == split
+    out = _run_c(capi, a, w, s, d_in, case.m, case.n, dtype=dtype, split_k=split, num_stages=stages)
+    checker(out, a, w, scale, d_in, f"m{m}_split{split}x{stages}")
+    again = _run_c(capi, a, w, s, d_in, case.m, case.n, dtype=dtype, split_k=split, num_stages=stages)
+    assert torch.equal(out, again)
+
+
 def test_padded_weight_rows_and_overwrite_mode(capi, dev, checker):
     from hf_rocm_kernels.benchmarks.skinny_gemm import workloads as wl
 
